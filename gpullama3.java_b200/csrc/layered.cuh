@@ -1,0 +1,459 @@
+// layered.cuh -- device kernels of "layered" plans: models described by a LIST of layers (each with its own mixer sizes and
+// feed-forward) instead of one repeated block, with BF16 weights and a 32-bit residual stream.  First user: Pibidra.
+//
+// Mechanisms, each with its constants as kernel arguments so other designs can pick them up:
+//   * k_norm_rows       sandwich norm: x += N(y; w_post), optional pass prologue (x += x0, x += step), out = N(x; w_pre),
+//                       N(v; w) = v / sqrt(mean(v^2) + eps) * (1 + w); also the embedding gather (x = scale * E[token]);
+//   * k_matvec_bf16     decode projection: BF16 weight rows streamed with 128-bit loads, FP32 activation and accumulator,
+//                       bias or gated-activation epilogue (gelu_tanh(g) * u);
+//   * k_gemm_f32 / k_gemm_bf16   prefill projections for any M, N, K: true FP32 on the CUDA cores, or BF16 operands on the
+//                       tensor cores (mma.sync m16n8k16, FP32 accumulation), same epilogues;
+//   * k_qk_prep         whole-projection RMS norm of q and of k (one statistic over ALL heads), K / V rows into the window ring;
+//   * k_window_attention  sliding-window attention over a ring cache with a soft logit cap, a learned bucketed distance bias
+//                       and a softmax whose denominator carries an extra exp(0) (a value-less sink), sigmoid output gate.
+// Everything the residual, the norms and the softmax touch is FP32; explicit fmaf keeps fused multiply-adds although the
+// translation unit is compiled with -fmad=false for the bit-exact GGUF kernels.
+#pragma once
+#include "common.cuh"
+#include <cuda_bf16.h>
+
+namespace ly {
+
+typedef __nv_bfloat16 bf16;
+
+enum { EPI_STORE = 0, EPI_GATED = 1 };   // C = A W^T (+ bias)  |  H = act(A Wg^T) * (A Wu^T) with W = [Wg; Wu] stacked by rows
+enum { ACT_GELU_TANH = 0, ACT_SILU = 1 };
+
+__device__ __forceinline__ float bf_lo(unsigned v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(unsigned v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ float act_apply(int act, float z) {
+    if (act == ACT_SILU) return z / (1.0f + expf(-z));
+    // tanh form of GELU: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+    const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+    return 0.5f * z * (1.0f + tanhf(u));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// Every thread of the block gets the total; red holds 32 floats.  blockDim.x is a multiple of 32.
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads(); // red may still be read from a previous call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : 0.0f;
+    return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nw ? red[lane] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Sandwich norm over rows.  One CTA per row; the row lives in shared memory between the passes.
+// ---------------------------------------------------------------------------------------------------------------------
+struct NormArgs {
+    float *x;            // [n][E] residual stream
+    float *x0;           // [n][E] embedding output kept for the loop passes (nullable)
+    const float *y;      // [n][E] sublayer output: x += N(y; w_post) (nullable)
+    const float *w_post; // [E]
+    const bf16 *emb;     // embedding table [vocab][E]: x = emb_scale * emb[token] (nullable)
+    const int *tokens;   // [n] (nullable: the step's own token)
+    const StepState *st;
+    float emb_scale;
+    int add_x0;          // pass prologue: x += x0
+    const float *step;   // pass prologue: x += step (nullable)
+    const float *w_pre;  // [E]: out = N(x; w_pre) (nullable)
+    float *out32;        // [n][E] (one of out32 / out16, or none)
+    bf16 *out16;
+    const int *gather;   // output row r is computed from x row gather[r] (only with y == emb == nullptr)
+    float *trace;        // [n][E]: copy of x after the post-norm part (nullable)
+    float eps;
+    int E;
+};
+#define LY_NORM_THREADS 256
+
+__global__ void __launch_bounds__(LY_NORM_THREADS) k_norm_rows(NormArgs a) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[32];
+    const int r = blockIdx.x, tid = threadIdx.x, E = a.E;
+    const size_t src = (size_t)(a.gather ? a.gather[r] : r) * E, dst = (size_t)r * E;
+    if (a.emb) {
+        const int token = a.tokens ? a.tokens[r] : a.st->token;
+        const bf16 *e = a.emb + (size_t)token * E;
+        for (int i = tid; i < E; i += LY_NORM_THREADS) {
+            const float v = __bfloat162float(e[i]) * a.emb_scale;
+            row[i] = v;
+            if (a.x0) a.x0[src + i] = v;
+        }
+    } else {
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = a.x[src + i];
+    }
+    if (a.y) {
+        float ss = 0.0f;
+        for (int i = tid; i < E; i += LY_NORM_THREADS) { const float v = a.y[src + i]; ss = fmaf(v, v, ss); }
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)E + a.eps);
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] += a.y[src + i] * inv * (1.0f + a.w_post[i]);
+    }
+    if (a.trace)
+        for (int i = tid; i < E; i += LY_NORM_THREADS) a.trace[src + i] = row[i];
+    if (a.add_x0)
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] += a.x0[src + i];
+    if (a.step)
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] += a.step[i];
+    if (!a.gather && (a.emb || a.y || a.add_x0 || a.step))
+        for (int i = tid; i < E; i += LY_NORM_THREADS) a.x[src + i] = row[i];
+    if (a.w_pre) {
+        float ss = 0.0f;
+        for (int i = tid; i < E; i += LY_NORM_THREADS) ss = fmaf(row[i], row[i], ss);
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)E + a.eps);
+        for (int i = tid; i < E; i += LY_NORM_THREADS) {
+            const float v = row[i] * inv * (1.0f + a.w_pre[i]);
+            if (a.out32) a.out32[dst + i] = v;
+            if (a.out16) a.out16[dst + i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode projection y = W x (+ bias) or h = act(Wg x) * (Wu x): one warp per output row, the activation staged once per
+// CTA in shared memory, weights streamed with 128-bit non-allocating loads.  W is [N][K] BF16 (EPI_GATED: [2N][K], gate rows
+// first).  K % 8 == 0 takes the vector path, anything else the scalar one.
+// ---------------------------------------------------------------------------------------------------------------------
+#define LY_MV_THREADS 256
+
+__device__ __forceinline__ float dot_row_bf16(const bf16 *__restrict__ w, const float *xs, int K, int lane, bool vec) {
+    float acc = 0.0f;
+    if (vec) {
+        for (int k = lane * 8; k < K; k += 256) {
+            const int4 q = ldg128_stream(w + k);
+            const float4 x0 = *reinterpret_cast<const float4 *>(xs + k), x1 = *reinterpret_cast<const float4 *>(xs + k + 4);
+            acc = fmaf(bf_lo((unsigned)q.x), x0.x, acc); acc = fmaf(bf_hi((unsigned)q.x), x0.y, acc);
+            acc = fmaf(bf_lo((unsigned)q.y), x0.z, acc); acc = fmaf(bf_hi((unsigned)q.y), x0.w, acc);
+            acc = fmaf(bf_lo((unsigned)q.z), x1.x, acc); acc = fmaf(bf_hi((unsigned)q.z), x1.y, acc);
+            acc = fmaf(bf_lo((unsigned)q.w), x1.z, acc); acc = fmaf(bf_hi((unsigned)q.w), x1.w, acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(__bfloat162float(w[k]), xs[k], acc);
+    }
+    return warp_sum(acc);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(LY_MV_THREADS) k_matvec_bf16(const bf16 *__restrict__ W, const float *__restrict__ bias, const float *__restrict__ x,
+                                                              float *__restrict__ y, int N, int K, int act) {
+    extern __shared__ __align__(16) float xs[];
+    for (int i = threadIdx.x; i < K; i += LY_MV_THREADS) xs[i] = x[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool vec = (K & 7) == 0;
+    for (int n = blockIdx.x * (LY_MV_THREADS / 32) + warp; n < N; n += gridDim.x * (LY_MV_THREADS / 32)) {
+        float v = dot_row_bf16(W + (size_t)n * K, xs, K, lane, vec);
+        if (EPI == EPI_GATED) {
+            const float u = dot_row_bf16(W + (size_t)(N + n) * K, xs, K, lane, vec);
+            v = act_apply(act, v) * u;
+        } else if (bias) v += bias[n];
+        if (lane == 0) y[n] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Prefill projection in true FP32 (no tensor cores): C[M][N] = A[M][K] W[N][K]^T.  64 x 64 x 16 tiles, 4 x 4 per thread.
+// OUT_T = float or bf16 (the gated epilogue feeds the next GEMM).
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ void store_out(T *p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int EPI, typename OUT_T>
+__global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, const bf16 *__restrict__ W, const float *__restrict__ bias,
+                                                   OUT_T *__restrict__ C, int M, int N, int K, int ldc, int act) {
+    constexpr int BM = 64, BN = 64, BK = 16, NB = EPI == EPI_GATED ? 2 : 1;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Bs[NB][BK][BN + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[NB][4][4];
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[b][i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int e = tid; e < BM * BK; e += 256) {
+            const int r = e / BK, c = e % BK;
+            const int m = m0 + r, k = k0 + c;
+            As[c][r] = (m < M && k < K) ? A[(size_t)m * K + k] : 0.0f;
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+            for (int e = tid; e < BN * BK; e += 256) {
+                const int r = e / BK, c = e % BK;
+                const int n = n0 + r, k = k0 + c;
+                Bs[b][c][r] = (n < N && k < K) ? __bfloat162float(W[((size_t)b * N + n) * K + k]) : 0.0f;
+            }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float av[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                float bv[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) bv[j] = Bs[b][kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[b][i][j] = fmaf(av[i], bv[j], acc[b][i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v;
+            if (EPI == EPI_GATED) v = act_apply(act, acc[0][i][j]) * acc[NB - 1][i][j];
+            else v = acc[0][i][j] + (bias ? bias[n] : 0.0f);
+            store_out<OUT_T>(C + (size_t)m * ldc + n, v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Prefill projection on the tensor cores for ANY M, N, K: BF16 operands, FP32 accumulation (mma.sync.m16n8k16).  64 x 64 x 32
+// tiles, four warps of 32 x 32; operands staged through padded shared memory (row stride 80 bytes: conflict-free fragment
+// reads); out-of-range rows and the K tail are zero-filled.  The shapes the tcgen05 GEMM accepts go there instead.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// rows x 32 BF16 tile of a row-major [R][K] matrix into shared memory (stride 40 elements), zero-filled outside
+__device__ __forceinline__ void load_tile_bf16(bf16 (*dst)[40], const bf16 *__restrict__ src, int r0, int R, int k0, int K, bool vec, int tid, int nthreads) {
+    if (vec) { // 4 chunks of 8 elements per row
+        for (int e = tid; e < 64 * 4; e += nthreads) {
+            const int r = e >> 2, c = (e & 3) * 8;
+            int4 v = make_int4(0, 0, 0, 0);
+            if (r0 + r < R && k0 + c < K) v = *reinterpret_cast<const int4 *>(src + (size_t)(r0 + r) * K + k0 + c);
+            *reinterpret_cast<int4 *>(&dst[r][c]) = v;
+        }
+    } else {
+        for (int e = tid; e < 64 * 32; e += nthreads) {
+            const int r = e >> 5, c = e & 31;
+            dst[r][c] = (r0 + r < R && k0 + c < K) ? src[(size_t)(r0 + r) * K + k0 + c] : __float2bfloat16_rn(0.0f);
+        }
+    }
+}
+
+template <int EPI, typename OUT_T>
+__global__ void __launch_bounds__(128) k_gemm_bf16(const bf16 *__restrict__ A, const bf16 *__restrict__ W, const float *__restrict__ bias,
+                                                    OUT_T *__restrict__ C, int M, int N, int K, int ldc, int act) {
+    constexpr int NB = EPI == EPI_GATED ? 2 : 1;
+    __shared__ __align__(16) bf16 As[64][40];
+    __shared__ __align__(16) bf16 Bs[NB][64][40];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    const int g = lane >> 2, t = lane & 3;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    const bool vec = (K & 7) == 0;
+    float acc[NB][2][4][4];
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[b][i][j][e] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        load_tile_bf16(As, A, m0, M, k0, K, vec, tid, 128);
+#pragma unroll
+        for (int b = 0; b < NB; b++) load_tile_bf16(Bs[b], W + (size_t)b * N * K, n0, N, k0, K, vec, tid, 128);
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 32; kk += 16) {
+            unsigned af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int r = wm + i * 16 + g;
+                af[i][0] = *reinterpret_cast<const unsigned *>(&As[r][kk + 2 * t]);
+                af[i][1] = *reinterpret_cast<const unsigned *>(&As[r + 8][kk + 2 * t]);
+                af[i][2] = *reinterpret_cast<const unsigned *>(&As[r][kk + 2 * t + 8]);
+                af[i][3] = *reinterpret_cast<const unsigned *>(&As[r + 8][kk + 2 * t + 8]);
+            }
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    unsigned bfr[2];
+                    const int n = wn + j * 8 + g;
+                    bfr[0] = *reinterpret_cast<const unsigned *>(&Bs[b][n][kk + 2 * t]);
+                    bfr[1] = *reinterpret_cast<const unsigned *>(&Bs[b][n][kk + 2 * t + 8]);
+#pragma unroll
+                    for (int i = 0; i < 2; i++) mma_bf16_16816(acc[b][i][j], af[i], bfr);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int m = m0 + wm + i * 16 + g + (e >> 1) * 8;
+                const int n = n0 + wn + j * 8 + 2 * t + (e & 1);
+                if (m >= M || n >= N) continue;
+                float v;
+                if (EPI == EPI_GATED) v = act_apply(act, acc[0][i][j][e]) * acc[NB - 1][i][j][e];
+                else v = acc[0][i][j][e] + (bias ? bias[n] : 0.0f);
+                store_out<OUT_T>(C + (size_t)m * ldc + n, v);
+            }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention of a layer with a sliding window over a ring cache.
+// ---------------------------------------------------------------------------------------------------------------------
+struct WindowAttn {
+    int heads, kv_heads, dk, dv; // query heads, key/value heads, key size, value size
+    int window;                  // position i sees j with 0 <= i - j < window
+    int ring;                    // cache slots: position j lives in slot j % ring (ring >= window - 1 + rows of a step)
+    int bias_rows;               // rows of the distance table rel[bias_rows][heads]
+    float scale, softcap;        // e = softcap * tanh(scale * <q, k> / softcap) + rel[bucket[i - j]][h]   (softcap <= 0: no cap)
+    const float *rel;            // [bias_rows][heads] (nullable: no distance bias)
+    const int *bucket;           // [window]: table row of every distance the window admits (built on the host in double precision)
+    const float *qnorm, *knorm;  // whole-projection RMS norm weights [heads*dk], [kv_heads*dk], used as stored (nullable: no norm)
+    int sink;                    // 1: the softmax denominator carries one extra exp(0)
+    int gate;                    // 1: the output is multiplied by sigmoid(g), g the fourth block of the fused projection
+    float eps;
+};
+// Row layout of the fused projection output: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv | g: heads*dv]
+
+// One CTA per row: RMS statistics over the WHOLE q and the WHOLE k projection, q normalised in place, k / v into the ring.
+__global__ void __launch_bounds__(256) k_qk_prep(float *__restrict__ P, int ldp, WindowAttn a, float *__restrict__ kc, float *__restrict__ vc,
+                                                 const StepState *__restrict__ st) {
+    __shared__ float red[32];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
+    float *q = P + (size_t)r * ldp, *k = q + qd, *v = k + kd;
+    const int slot = (st->pos + r) % a.ring;
+    float qinv = 1.0f, kinv = 1.0f;
+    if (a.qnorm) {
+        float ss = 0.0f;
+        for (int i = tid; i < qd; i += 256) ss = fmaf(q[i], q[i], ss);
+        ss = block_sum(ss, red);
+        qinv = 1.0f / sqrtf(ss / (float)qd + a.eps);
+    }
+    if (a.knorm) {
+        float ss = 0.0f;
+        for (int i = tid; i < kd; i += 256) ss = fmaf(k[i], k[i], ss);
+        ss = block_sum(ss, red);
+        kinv = 1.0f / sqrtf(ss / (float)kd + a.eps);
+    }
+    for (int i = tid; i < qd; i += 256) q[i] = a.qnorm ? q[i] * qinv * a.qnorm[i] : q[i];
+    for (int i = tid; i < kd; i += 256) kc[(size_t)slot * kd + i] = a.knorm ? k[i] * kinv * a.knorm[i] : k[i];
+    for (int i = tid; i < vd; i += 256) vc[(size_t)slot * vd + i] = v[i];
+}
+
+// One CTA per (row, head): scores of the window into shared memory, softmax with the sink term, weighted value sum, gate.
+// Dynamic shared memory: dk + min(window, ring) + LY_ATT_THREADS floats.
+#define LY_ATT_THREADS 128
+template <typename OUT_T>
+__global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ kc,
+                                                                     const float *__restrict__ vc, const StepState *__restrict__ st,
+                                                                     OUT_T *__restrict__ out, int ldo) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[32];
+    const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
+    const int g = h / (a.heads / a.kv_heads);
+    const int pos = st->pos + r;
+    const int lo = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
+    const int nk = pos - lo + 1;
+    float *qs = sm, *sc = sm + a.dk, *part = sc + a.window;
+    const float *q = P + (size_t)r * ldp + (size_t)h * a.dk;
+    for (int i = tid; i < a.dk; i += LY_ATT_THREADS) qs[i] = q[i];
+    __syncthreads();
+    // scores: one key per thread
+    float mx = 0.0f; // the sink's logit; without a sink the maximum is taken over the keys alone
+    if (!a.sink) mx = -INFINITY;
+    const bool vec = (a.dk & 3) == 0 && (kd & 3) == 0;
+    for (int j = tid; j < nk; j += LY_ATT_THREADS) {
+        const int p = lo + j;
+        const float *kr = kc + (size_t)(p % a.ring) * kd + (size_t)g * a.dk;
+        float d = 0.0f;
+        if (vec) {
+            for (int i = 0; i < a.dk; i += 4) {
+                const float4 kv = *reinterpret_cast<const float4 *>(kr + i);
+                d = fmaf(qs[i], kv.x, d); d = fmaf(qs[i + 1], kv.y, d); d = fmaf(qs[i + 2], kv.z, d); d = fmaf(qs[i + 3], kv.w, d);
+            }
+        } else {
+            for (int i = 0; i < a.dk; i++) d = fmaf(qs[i], kr[i], d);
+        }
+        float e = d * a.scale;
+        if (a.softcap > 0.0f) e = a.softcap * tanhf(e / a.softcap);
+        if (a.rel) e += a.rel[(size_t)a.bucket[pos - p] * a.heads + h];
+        sc[j] = e;
+        mx = fmaxf(mx, e);
+    }
+    mx = block_max(mx, red);
+    float sum = 0.0f;
+    for (int j = tid; j < nk; j += LY_ATT_THREADS) {
+        const float w = expf(sc[j] - mx);
+        sc[j] = w;
+        sum += w;
+    }
+    sum = block_sum(sum, red); // also orders the sc[] writes before the reads below
+    const float inv = 1.0f / (sum + (a.sink ? expf(-mx) : 0.0f));
+    // weighted values: thread groups of dv lanes take every groups-th key
+    const int groups = a.dv >= LY_ATT_THREADS ? 1 : LY_ATT_THREADS / a.dv;
+    const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * a.dv;
+    for (int d0 = 0; d0 < a.dv; d0 += LY_ATT_THREADS) {
+        const int grp = a.dv >= LY_ATT_THREADS ? 0 : tid / a.dv;
+        const int d = a.dv >= LY_ATT_THREADS ? d0 + tid : tid % a.dv;
+        float acc = 0.0f;
+        if (d < a.dv && grp < groups)
+            for (int j = grp; j < nk; j += groups) acc = fmaf(sc[j], vc[(size_t)((lo + j) % a.ring) * vd + (size_t)g * a.dv + d], acc);
+        if (groups > 1) {
+            part[tid] = acc;
+            __syncthreads();
+            if (tid < a.dv) {
+                for (int k = 1; k < groups; k++) acc += part[tid + k * a.dv];
+            }
+            __syncthreads();
+        }
+        if (grp == 0 && d < a.dv) {
+            float o = acc * inv;
+            if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d]));
+            store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d, o);
+        }
+    }
+}
+
+} // namespace ly

@@ -1,0 +1,516 @@
+// layered_plan.cuh -- host side of layered plans (included by plan.cu after its helpers): weight upload, the per-run window
+// ring caches, the decode graph and the chunked prefill of models given as a list of layer specifications.
+//
+// Execution order.  The layer list is unrolled into RUNS: a loop block [start, stop) that executes `times` passes over the same
+// weights contributes times * (stop - start) runs, and every run owns a key/value ring of its own (same weights, different
+// history).  A pass starts with x += x0 (the embedding output; not on the first pass) and x += step[pass].
+//
+// Cache.  A run's ring has `ring` slots; position j lives in slot j % ring.  With ring >= window - 1 + (rows of one step) a
+// step never overwrites a key one of its own rows still needs, so memory is bounded by the window, not by the context; a
+// position is only ever read through an index range derived from the CURRENT position, so recycled slots and a new request
+// starting at position 0 need no clearing.
+//
+// Kernel sequence of one run (decode: one row, captured once into a CUDA graph driven by the device-resident StepState;
+// prefill: n rows per launch): norm (post-norm + residual of the previous sublayer, pass prologue, pre-norm) -> fused
+// q|k|v|gate projection (+bias) -> whole-projection q/k norm + ring write -> window attention (+gate) -> output projection ->
+// norm -> gated feed-forward projection (activation in the epilogue) -> down projection.
+#pragma once
+#include "layered.cuh"
+
+struct LyLayer {
+    b200_layer_spec s{};
+    int qd = 0, kd = 0, vd = 0, gd = 0, P = 0; // fused projection: q | k | v | gate rows
+    ly::bf16 *w_proj = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_down = nullptr;
+    float *b_proj = nullptr;
+    float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *qnorm = nullptr, *knorm = nullptr, *rel = nullptr;
+    int *bucket = nullptr;
+};
+struct LyRun {
+    int layer = 0, pass = -1;
+    bool first = false; // first layer of a loop pass
+    float *kc = nullptr, *vc = nullptr;
+};
+struct Layered {
+    b200_layered_config c{};
+    std::vector<LyLayer> layers;
+    std::vector<LyRun> runs;
+    ly::bf16 *emb = nullptr, *head = nullptr;
+    float *final_norm = nullptr, *step = nullptr;
+    int cap = 1, ring = 0, max_window = 1, logit_rows = 1;
+    int maxP = 0, maxO = 0, maxF = 0;
+    bool f32 = false, has_loop = false;
+    float *X = nullptr, *X0 = nullptr, *Y = nullptr, *PROJ = nullptr, *A32 = nullptr, *ATT32 = nullptr, *H32 = nullptr, *LOG = nullptr;
+    ly::bf16 *A16 = nullptr, *ATT16 = nullptr, *H16 = nullptr;
+    int *tok = nullptr, *rows = nullptr;
+    StepState *st_pf = nullptr;
+    float *trace = nullptr; // [runs][cap][width], allocated on first use
+    int smem_max = 0;
+};
+
+static int ly_vec_f32(b200_plan *p, const b200_tensor *tensors, int nt, const std::string &name, int64_t n, float **dst, bool required = true) {
+    const b200_tensor *t = find(tensors, nt, name);
+    if (!t) {
+        if (!required) { *dst = nullptr; return B200_OK; }
+        return fail(p, B200_ERR_BAD_ARG, "missing tensor %s", name.c_str());
+    }
+    if (n_elems(t) != n) return fail(p, B200_ERR_BAD_ARG, "tensor %s has %lld elements, expected %lld", name.c_str(), (long long)n_elems(t), (long long)n);
+    std::vector<float> h((size_t)n);
+    if (t->ggml_type == B200_GGML_BF16) {
+        const uint16_t *s = (const uint16_t *)t->data;
+        for (int64_t i = 0; i < n; i++) { uint32_t u = (uint32_t)s[i] << 16; memcpy(&h[i], &u, 4); }
+    } else if (t->ggml_type == B200_GGML_F32) memcpy(h.data(), t->data, (size_t)n * 4);
+    else return fail(p, B200_ERR_UNSUPPORTED, "tensor %s: type %d (vectors are BF16 or F32)", name.c_str(), t->ggml_type);
+    int rc;
+    if ((rc = dalloc(p, dst, (size_t)n * 4))) return rc;
+    CK(cudaMemcpy(*dst, h.data(), (size_t)n * 4, cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+// rows x cols BF16 matrix into dst at row offset row_off, through the plan's upload pipeline
+static int ly_mat(b200_plan *p, const b200_tensor *tensors, int nt, const std::string &name, int rows, int cols, ly::bf16 *dst, int row_off) {
+    const b200_tensor *t = find(tensors, nt, name);
+    if (!t) return fail(p, B200_ERR_BAD_ARG, "missing tensor %s", name.c_str());
+    if (t->ggml_type != B200_GGML_BF16) return fail(p, B200_ERR_UNSUPPORTED, "tensor %s: type %d (layered plans take BF16 matrices)", name.c_str(), t->ggml_type);
+    if (t->n_dims != 2 || t->dims[0] != cols || t->dims[1] != rows)
+        return fail(p, B200_ERR_BAD_ARG, "tensor %s is not [%d][%d]", name.c_str(), rows, cols);
+    const size_t bytes = (size_t)rows * cols * 2;
+    if (p->up.on) return up_h2d(p, dst + (size_t)row_off * cols, t->data, bytes);
+    CK(cudaMemcpy(dst + (size_t)row_off * cols, t->data, bytes, cudaMemcpyHostToDevice));
+    p->up.h2d_bytes += (int64_t)bytes;
+    return B200_OK;
+}
+
+// Distance -> table row: exact below rows/2, logarithmic up to `far`, the last row beyond (evaluated in double on the host).
+static int ly_bucket(int n, int rows, double far) {
+    const int half = rows / 2;
+    if (n < half) return n;
+    const int b = half + (int)floor(log((double)n / half) / log(far / half) * (rows - half));
+    return b < rows - 1 ? b : rows - 1;
+}
+
+static void ly_free(b200_plan *p) {
+    delete p->ly;
+    p->ly = nullptr;
+}
+
+static size_t ly_att_smem(const b200_layer_spec &s, int ring) {
+    (void)ring;
+    return (size_t)(s.key_dim + s.window + LY_ATT_THREADS) * 4;
+}
+
+static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
+    ly::WindowAttn a{};
+    a.heads = L.s.heads; a.kv_heads = L.s.kv_heads; a.dk = L.s.key_dim; a.dv = L.s.value_dim;
+    a.window = L.s.window; a.ring = Y.ring; a.bias_rows = L.s.bias_rows;
+    a.scale = L.s.score_scale; a.softcap = L.s.softcap;
+    a.rel = L.rel; a.bucket = L.bucket; a.qnorm = L.qnorm; a.knorm = L.knorm;
+    a.sink = L.s.sink; a.gate = L.s.gate; a.eps = Y.c.norm_eps;
+    return a;
+}
+
+// C[n][N] = A[n][K] W^T with the epilogue EPI; decode (n == 1 through the graph) streams the rows, prefill takes a GEMM.
+template <int EPI>
+static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const ly::bf16 *a16, const ly::bf16 *W, const float *bias, int N, int K,
+                      float *c32, ly::bf16 *c16, int ldc, int act) {
+    Layered &Y = *p->ly;
+    if (decode) {
+        const int warps = LY_MV_THREADS / 32;
+        int grid = (N + warps - 1) / warps;
+        return launch_k(p, false, ly::k_matvec_bf16<EPI>, dim3(grid), dim3(LY_MV_THREADS), (size_t)K * 4, W, bias, a32, c32, N, K, act);
+    }
+    dim3 grid((N + 63) / 64, (n + 63) / 64);
+    if (Y.f32) return launch_k(p, false, ly::k_gemm_f32<EPI, float>, grid, dim3(256), (size_t)0, a32, W, bias, c32, n, N, K, ldc, act);
+    if (c16) return launch_k(p, false, ly::k_gemm_bf16<EPI, ly::bf16>, grid, dim3(128), (size_t)0, a16, W, bias, c16, n, N, K, ldc, act);
+    return launch_k(p, false, ly::k_gemm_bf16<EPI, float>, grid, dim3(128), (size_t)0, a16, W, bias, c32, n, N, K, ldc, act);
+}
+
+// Enqueue the forward of n rows on p->stream.  decode: the single-token step (row 0, position and token from *st).
+// with_head (decode only): final norm + classifier into p->logits.  Prefill leaves the finished residual rows in X.
+static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, const int *tokens, bool with_head, float *trace, int *launches) {
+    Layered &Y = *p->ly;
+    const int E = Y.c.width;
+    const bool h16 = !decode && !Y.f32; // prefill in BF16 mode rounds GEMM operands to BF16
+    int nl = 0, rc;
+    const float *pend_y = nullptr, *pend_w = nullptr;
+    float *pend_trace = nullptr;
+    auto norm = [&](bool embed, bool add_x0, const float *step, const float *w_pre) {
+        ly::NormArgs a{};
+        a.x = Y.X; a.x0 = Y.has_loop ? Y.X0 : nullptr;
+        a.y = pend_y; a.w_post = pend_w;
+        a.emb = embed ? Y.emb : nullptr; a.tokens = tokens; a.st = st; a.emb_scale = Y.c.embedding_scale;
+        a.add_x0 = add_x0 ? 1 : 0; a.step = step; a.w_pre = w_pre;
+        a.out32 = w_pre && !h16 ? Y.A32 : nullptr; a.out16 = w_pre && h16 ? Y.A16 : nullptr;
+        a.gather = nullptr; a.trace = pend_trace; a.eps = Y.c.norm_eps; a.E = E;
+        pend_y = pend_w = nullptr; pend_trace = nullptr;
+        nl++;
+        return launch_k(p, false, ly::k_norm_rows, dim3(n), dim3(LY_NORM_THREADS), (size_t)E * 4, a);
+    };
+    for (size_t r = 0; r < Y.runs.size(); r++) {
+        const LyRun &R = Y.runs[r];
+        const LyLayer &L = Y.layers[R.layer];
+        if ((rc = norm(r == 0, R.first && R.pass > 0, R.first ? Y.step + (size_t)R.pass * E : nullptr, L.norm1))) return rc;
+        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, L.b_proj, L.P, E, Y.PROJ, nullptr, Y.maxP, 0))) return rc;
+        nl++;
+        const ly::WindowAttn wa = ly_attn_args(Y, L);
+        if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, R.kc, R.vc, st))) return rc;
+        nl++;
+        const size_t asm_ = ly_att_smem(L.s, Y.ring);
+        if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
+                               (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd);
+        else rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
+                           (const float *)R.kc, (const float *)R.vc, st, Y.ATT32, L.gd);
+        if (rc) return rc;
+        nl++;
+        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.ATT32, Y.ATT16, L.w_o, nullptr, E, L.gd, Y.Y, nullptr, E, 0))) return rc;
+        nl++;
+        pend_y = Y.Y; pend_w = L.norm1b;
+        if (L.s.ff_kind == B200_FF_DENSE_GATED) {
+            if ((rc = norm(false, false, nullptr, L.norm2))) return rc;
+            const int F = L.s.ff_dim;
+            if ((rc = ly_project<ly::EPI_GATED>(p, decode, n, Y.A32, Y.A16, L.w_gu, nullptr, F, E, Y.H32, h16 ? Y.H16 : nullptr, F, L.s.ff_act))) return rc;
+            nl++;
+            if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.H32, Y.H16, L.w_down, nullptr, E, F, Y.Y, nullptr, E, 0))) return rc;
+            nl++;
+            pend_y = Y.Y; pend_w = L.norm2b;
+        }
+        pend_trace = trace ? trace + r * (size_t)Y.cap * E : nullptr;
+    }
+    if (decode) {
+        if (with_head) {
+            if ((rc = norm(false, false, nullptr, Y.final_norm))) return rc;
+            if ((rc = ly_project<ly::EPI_STORE>(p, true, 1, Y.A32, nullptr, Y.head, nullptr, Y.c.vocab_size, E, p->logits, nullptr, Y.c.vocab_size, 0))) return rc;
+            nl++;
+        } else if ((rc = norm(false, false, nullptr, nullptr))) return rc;
+        if ((rc = launch_k(p, false, k_argmax_advance, dim3(1), dim3(1024), (size_t)0, (const float *)p->logits, Y.c.vocab_size, p->st, (const int *)p->seq_tokens,
+                           p->out_ids, with_head ? 1 : 0, (const float *)nullptr, (const int *)nullptr, 0, TraceBuf{nullptr, 0, 0}, p->tp, -1))) return rc;
+        nl++;
+    } else if ((rc = norm(false, false, nullptr, nullptr))) return rc;
+    if (launches) *launches = nl;
+    return B200_OK;
+}
+
+static int ly_capture(b200_plan *p, bool with_head, cudaGraphExec_t *exec, int *launches) {
+    cudaGraph_t g = nullptr;
+    CK(cudaStreamBeginCapture(p->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = ly_enqueue(p, true, 1, p->st, nullptr, with_head, nullptr, launches);
+    cudaError_t e = cudaStreamEndCapture(p->stream, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return fail(p, B200_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(p, B200_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    return B200_OK;
+}
+
+static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_layer_spec *specs, const b200_tensor *tensors, int nt) {
+    Layered *Yp = new Layered();
+    p->ly = Yp;
+    Layered &Y = *Yp;
+    Y.c = *cfg;
+    const b200_layered_config &c = Y.c;
+    if (c.arch != B200_ARCH_PIBIDRA) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
+    if (c.width <= 0 || c.vocab_size <= 0 || c.n_layers <= 0 || c.context_length <= 0) return fail(p, B200_ERR_BAD_ARG, "width, vocabulary, layers and context must be positive");
+    if (c.compute != B200_COMPUTE_BF16 && c.compute != B200_COMPUTE_F32) return fail(p, B200_ERR_BAD_ARG, "compute must be B200_COMPUTE_BF16 or B200_COMPUTE_F32");
+    Y.f32 = c.compute == B200_COMPUTE_F32;
+    Y.has_loop = c.loop_times >= 0;
+    if (Y.has_loop && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop)) return fail(p, B200_ERR_BAD_ARG, "loop [%d, %d) outside the %d layers", c.loop_start, c.loop_stop, c.n_layers);
+    const int E = c.width;
+    // the fields of b200_config the shared entry points read
+    p->cfg.arch = c.arch; p->cfg.dim = E; p->cfg.n_layers = c.n_layers; p->cfg.vocab_size = c.vocab_size; p->cfg.context_length = c.context_length;
+    p->cfg.rms_norm_eps = c.norm_eps; p->cfg.tp_rank = 0; p->cfg.tp_size = 1;
+    p->tp.rank = 0; p->tp.n = 1;
+    p->wtype = B200_GGML_BF16;
+    p->pd_why = "layered plans decode through the CUDA graph";
+    p->prefill.why = "layered plans prefill through b200_forward_batch_prefill / b200_forward_batch_logits in the plan's compute mode";
+
+    CK(cudaSetDevice(p->device));
+    CK(cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking));
+    CK(cudaEventCreate(&p->ev0));
+    CK(cudaEventCreate(&p->ev1));
+    CK(cudaDeviceGetAttribute(&p->n_sms, cudaDevAttrMultiProcessorCount, p->device));
+    CK(cudaDeviceGetAttribute(&Y.smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, p->device));
+    int rc;
+    Y.cap = p->prefill_batch > 1 ? p->prefill_batch : 1;
+    Y.layers.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; l++) {
+        LyLayer &L = Y.layers[l];
+        L.s = specs[l];
+        const b200_layer_spec &s = L.s;
+        if (s.mixer != B200_MIXER_WINDOW_ATTENTION) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d", l, s.mixer);
+        if (s.heads <= 0 || s.kv_heads <= 0 || s.heads % s.kv_heads || s.key_dim <= 0 || s.value_dim <= 0 || s.window <= 0)
+            return fail(p, B200_ERR_BAD_ARG, "layer %d: heads %d / kv heads %d / key %d / value %d / window %d", l, s.heads, s.kv_heads, s.key_dim, s.value_dim, s.window);
+        if (s.bias_rows < 0 || (s.bias_rows > 0 && (s.bias_rows < 2 || !(s.bias_far > s.bias_rows / 2))))
+            return fail(p, B200_ERR_BAD_ARG, "layer %d: distance table of %d rows up to %g", l, s.bias_rows, (double)s.bias_far);
+        if (s.ff_kind != B200_FF_NONE && s.ff_kind != B200_FF_DENSE_GATED) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: feed-forward kind %d", l, s.ff_kind);
+        if (s.ff_kind == B200_FF_DENSE_GATED && (s.ff_dim <= 0 || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU)))
+            return fail(p, B200_ERR_BAD_ARG, "layer %d: feed-forward width %d / activation %d", l, s.ff_dim, s.ff_act);
+        L.qd = s.heads * s.key_dim; L.kd = s.kv_heads * s.key_dim; L.vd = s.kv_heads * s.value_dim; L.gd = s.heads * s.value_dim;
+        L.P = L.qd + L.kd + L.vd + (s.gate ? L.gd : 0);
+        if (L.P > Y.maxP) Y.maxP = L.P;
+        if (L.gd > Y.maxO) Y.maxO = L.gd;
+        if (s.ff_kind == B200_FF_DENSE_GATED && s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
+        if (s.window > Y.max_window) Y.max_window = s.window;
+    }
+    {
+        int maxK = E > Y.maxO ? E : Y.maxO;
+        if (Y.maxF > maxK) maxK = Y.maxF;
+        size_t need = (size_t)maxK * 4;
+        for (const LyLayer &L : Y.layers) if (ly_att_smem(L.s, 0) > need) need = ly_att_smem(L.s, 0);
+        if (need > (size_t)Y.smem_max) return fail(p, B200_ERR_UNSUPPORTED, "a row of %zu bytes (widest activation or window) exceeds the %d bytes of shared memory a CTA can hold", need, Y.smem_max);
+        static bool attrs = false; // per function and process-wide, like plan.cu's set_smem_attrs
+        if (!attrs) {
+            CK(set_max_dyn(ly::k_norm_rows, Y.smem_max));
+            CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_STORE>, Y.smem_max));
+            CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_GATED>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention<float>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention<ly::bf16>, Y.smem_max));
+            attrs = true;
+        }
+    }
+    // ring: a step of `cap` rows must not overwrite keys its first rows still see; never more slots than positions
+    {
+        long long want = (long long)Y.max_window - 1 + Y.cap;
+        Y.ring = (int)(want < c.context_length ? want : c.context_length);
+        if (Y.ring < 1) Y.ring = 1;
+    }
+    // unroll the loop into runs
+    for (int l = 0; l < c.n_layers;) {
+        if (Y.has_loop && l == c.loop_start && c.loop_stop > c.loop_start) {
+            for (int t = 0; t < c.loop_times; t++)
+                for (int k = c.loop_start; k < c.loop_stop; k++) { LyRun R; R.layer = k; R.pass = t; R.first = k == c.loop_start; Y.runs.push_back(R); }
+            l = c.loop_stop;
+            continue;
+        }
+        LyRun R; R.layer = l++; Y.runs.push_back(R);
+    }
+    if (Y.runs.empty()) return fail(p, B200_ERR_BAD_ARG, "the loop leaves no layer to run");
+
+    const auto t_up0 = std::chrono::steady_clock::now();
+    if ((rc = up_init(p, 256))) return rc;
+    struct UpGuard { b200_plan *pl; ~UpGuard() { up_destroy(pl); } } guard{p};
+    if ((rc = dalloc(p, &Y.emb, (size_t)c.vocab_size * E * 2))) return rc;
+    if ((rc = ly_mat(p, tensors, nt, "embed", c.vocab_size, E, Y.emb, 0))) return rc;
+    if ((rc = dalloc(p, &Y.head, (size_t)c.vocab_size * E * 2))) return rc;
+    if ((rc = ly_mat(p, tensors, nt, "head", c.vocab_size, E, Y.head, 0))) return rc;
+    if ((rc = ly_vec_f32(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
+    if (Y.has_loop && c.loop_times > 0)
+        if ((rc = ly_vec_f32(p, tensors, nt, "loop.step", (int64_t)c.loop_times * E, &Y.step))) return rc;
+    for (int l = 0; l < c.n_layers; l++) {
+        LyLayer &L = Y.layers[l];
+        const b200_layer_spec &s = L.s;
+        const std::string pre = "l" + std::to_string(l) + ".", mx = pre + "mix.", ff = pre + "mlp.";
+        if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1", E, &L.norm1))) return rc;
+        if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1b", E, &L.norm1b))) return rc;
+        if ((rc = dalloc(p, &L.w_proj, (size_t)L.P * E * 2))) return rc;
+        if ((rc = ly_mat(p, tensors, nt, mx + "q", L.qd, E, L.w_proj, 0))) return rc;
+        if ((rc = ly_mat(p, tensors, nt, mx + "k", L.kd, E, L.w_proj, L.qd))) return rc;
+        if ((rc = ly_mat(p, tensors, nt, mx + "v", L.vd, E, L.w_proj, L.qd + L.kd))) return rc;
+        if (s.gate && (rc = ly_mat(p, tensors, nt, mx + "g", L.gd, E, L.w_proj, L.qd + L.kd + L.vd))) return rc;
+        { // biases of q, k, v in one vector; the gate has none
+            std::vector<float> b((size_t)L.P, 0.0f);
+            const char *nm[3] = {"q.b", "k.b", "v.b"};
+            const int off[3] = {0, L.qd, L.qd + L.kd}, len[3] = {L.qd, L.kd, L.vd};
+            bool any = false;
+            for (int k = 0; k < 3; k++) {
+                const b200_tensor *t = find(tensors, nt, mx + nm[k]);
+                if (!t) { if (s.qkv_bias) return fail(p, B200_ERR_BAD_ARG, "missing tensor %s%s", mx.c_str(), nm[k]); continue; }
+                if (n_elems(t) != len[k] || t->ggml_type != B200_GGML_BF16) return fail(p, B200_ERR_BAD_ARG, "tensor %s%s: %d BF16 values expected", mx.c_str(), nm[k], len[k]);
+                const uint16_t *src = (const uint16_t *)t->data;
+                for (int i = 0; i < len[k]; i++) { uint32_t u = (uint32_t)src[i] << 16; memcpy(&b[off[k] + i], &u, 4); }
+                any = true;
+            }
+            if (any && s.qkv_bias) {
+                if ((rc = dalloc(p, &L.b_proj, (size_t)L.P * 4))) return rc;
+                CK(cudaMemcpy(L.b_proj, b.data(), (size_t)L.P * 4, cudaMemcpyHostToDevice));
+            }
+        }
+        if (s.qk_norm) {
+            if ((rc = ly_vec_f32(p, tensors, nt, mx + "q.norm", L.qd, &L.qnorm))) return rc;
+            if ((rc = ly_vec_f32(p, tensors, nt, mx + "k.norm", L.kd, &L.knorm))) return rc;
+        }
+        if (s.bias_rows > 0) {
+            if ((rc = ly_vec_f32(p, tensors, nt, mx + "rel", (int64_t)s.bias_rows * s.heads, &L.rel))) return rc;
+            std::vector<int> bk((size_t)s.window);
+            for (int n = 0; n < s.window; n++) bk[n] = ly_bucket(n, s.bias_rows, (double)s.bias_far);
+            if ((rc = dalloc(p, &L.bucket, (size_t)s.window * 4))) return rc;
+            CK(cudaMemcpy(L.bucket, bk.data(), (size_t)s.window * 4, cudaMemcpyHostToDevice));
+        }
+        if ((rc = dalloc(p, &L.w_o, (size_t)E * L.gd * 2))) return rc;
+        if ((rc = ly_mat(p, tensors, nt, mx + "o", E, L.gd, L.w_o, 0))) return rc;
+        if (s.ff_kind == B200_FF_DENSE_GATED) {
+            const int F = s.ff_dim;
+            if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm2", E, &L.norm2))) return rc;
+            if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm2b", E, &L.norm2b))) return rc;
+            if ((rc = dalloc(p, &L.w_gu, (size_t)2 * F * E * 2))) return rc;
+            if ((rc = ly_mat(p, tensors, nt, ff + "gate", F, E, L.w_gu, 0))) return rc;
+            if ((rc = ly_mat(p, tensors, nt, ff + "up", F, E, L.w_gu, F))) return rc;
+            if ((rc = dalloc(p, &L.w_down, (size_t)E * F * 2))) return rc;
+            if ((rc = ly_mat(p, tensors, nt, ff + "down", E, F, L.w_down, 0))) return rc;
+        }
+    }
+    if (p->up.on) CK(cudaStreamSynchronize(p->up.copy));
+    p->up.total_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_up0).count();
+
+    // per-run rings
+    for (LyRun &R : Y.runs) {
+        const LyLayer &L = Y.layers[R.layer];
+        if ((rc = dalloc(p, &R.kc, (size_t)Y.ring * L.kd * 4))) return rc;
+        if ((rc = dalloc(p, &R.vc, (size_t)Y.ring * L.vd * 4))) return rc;
+        CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kd * 4));
+        CK(cudaMemset(R.vc, 0, (size_t)Y.ring * L.vd * 4));
+    }
+    // activations
+    const size_t cap = (size_t)Y.cap, rows32 = Y.f32 ? cap : 1;
+    const int maxF = Y.maxF > 0 ? Y.maxF : 1;
+    if ((rc = dalloc(p, &Y.X, cap * E * 4))) return rc;
+    if (Y.has_loop && (rc = dalloc(p, &Y.X0, cap * E * 4))) return rc;
+    if ((rc = dalloc(p, &Y.Y, cap * E * 4))) return rc;
+    if ((rc = dalloc(p, &Y.PROJ, cap * Y.maxP * 4))) return rc;
+    if ((rc = dalloc(p, &Y.A32, rows32 * E * 4))) return rc;
+    if ((rc = dalloc(p, &Y.ATT32, rows32 * Y.maxO * 4))) return rc;
+    if ((rc = dalloc(p, &Y.H32, rows32 * maxF * 4))) return rc;
+    if (!Y.f32) {
+        if ((rc = dalloc(p, &Y.A16, cap * E * 2))) return rc;
+        if ((rc = dalloc(p, &Y.ATT16, cap * Y.maxO * 2))) return rc;
+        if ((rc = dalloc(p, &Y.H16, cap * maxF * 2))) return rc;
+    }
+    Y.logit_rows = Y.cap < 128 ? Y.cap : 128;
+    if ((rc = dalloc(p, &Y.LOG, (size_t)Y.logit_rows * c.vocab_size * 4))) return rc;
+    if ((rc = dalloc(p, &Y.tok, cap * 4))) return rc;
+    if ((rc = dalloc(p, &Y.rows, cap * 4))) return rc;
+    if ((rc = dalloc(p, &Y.st_pf, sizeof(StepState)))) return rc;
+    CK(cudaMemset(Y.st_pf, 0, sizeof(StepState)));
+    // what the shared single-token entry points use
+    if ((rc = dalloc(p, &p->logits, (size_t)sampler_padded(c.vocab_size) * 4))) return rc;
+    CK(cudaMemset(p->logits, 0, (size_t)sampler_padded(c.vocab_size) * 4));
+    if ((rc = dalloc(p, &p->smp_indices, (size_t)c.vocab_size * 4))) return rc;
+    if ((rc = dalloc(p, &p->smp_out, 8 * 4))) return rc;
+    p->seq_cap = (c.context_length > Y.cap ? c.context_length : Y.cap) + 8;
+    if ((rc = dalloc(p, &p->st, sizeof(StepState)))) return rc;
+    if ((rc = dalloc(p, &p->seq_tokens, (size_t)p->seq_cap * 4))) return rc;
+    if ((rc = dalloc(p, &p->out_ids, (size_t)p->seq_cap * 4))) return rc;
+    CK(cudaMemset(p->st, 0, sizeof(StepState)));
+    CK(cudaMemset(p->seq_tokens, 0, (size_t)p->seq_cap * 4));
+    CK(cudaMallocHost(&p->h_st, sizeof(StepState)));
+    CK(cudaMallocHost(&p->h_ids, (size_t)p->seq_cap * 4));
+    p->x = Y.X;
+    if ((rc = ly_capture(p, true, &p->g_decode, &p->launches_decode))) return rc;
+    if ((rc = ly_capture(p, false, &p->g_prefill, nullptr))) return rc;
+    CK(cudaStreamSynchronize(p->stream));
+    return B200_OK;
+}
+
+// One chunk of n <= cap tokens at positions start_pos..: fills the rings; optionally returns the logits of selected rows and
+// the residual stream after every run ([runs][n][width]).
+static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, const int32_t *rows, int n_rows, float *logits_out, float *trace_out) {
+    Layered &Y = *p->ly;
+    const int E = Y.c.width, V = Y.c.vocab_size;
+    if (n > Y.cap) return fail(p, B200_ERR_BAD_ARG, "chunk of %d tokens exceeds prefill_batch_size %d", n, Y.cap);
+    if (start_pos < 0 || start_pos + n > Y.c.context_length) return fail(p, B200_ERR_BAD_ARG, "positions %d..%d outside the context (%d)", start_pos, start_pos + n - 1, Y.c.context_length);
+    for (int i = 0; i < n; i++)
+        if (tokens[i] < 0 || tokens[i] >= V) return fail(p, B200_ERR_BAD_ARG, "token %d out of range", tokens[i]);
+    for (int i = 0; i < n_rows; i++)
+        if (rows[i] < 0 || rows[i] >= n) return fail(p, B200_ERR_BAD_ARG, "row %d outside the chunk of %d tokens", rows[i], n);
+    if (n_rows > 0 && (!rows || !logits_out)) return fail(p, B200_ERR_BAD_ARG, "rows without an output buffer");
+    int rc;
+    if (trace_out && !Y.trace)
+        if ((rc = dalloc(p, &Y.trace, Y.runs.size() * (size_t)Y.cap * E * 4))) return rc;
+    memcpy(p->h_ids, tokens, (size_t)n * 4);
+    CK(cudaMemcpyAsync(Y.tok, p->h_ids, (size_t)n * 4, cudaMemcpyHostToDevice, p->stream));
+    StepState *h = p->h_st;
+    memset(h, 0, sizeof(StepState));
+    h->token = tokens[0]; h->pos = start_pos;
+    CK(cudaMemcpyAsync(Y.st_pf, h, sizeof(StepState), cudaMemcpyHostToDevice, p->stream));
+    CK(cudaEventRecord(p->ev0, p->stream));
+    if ((rc = ly_enqueue(p, false, n, Y.st_pf, Y.tok, false, trace_out ? Y.trace : nullptr, &p->launches_prefill))) return rc;
+    CK(cudaEventRecord(p->ev1, p->stream));
+    CK(cudaStreamSynchronize(p->stream)); // h_ids / h_st are reused below
+    CK(cudaEventElapsedTime(&p->prefill_ms, p->ev0, p->ev1));
+    for (int r0 = 0; r0 < n_rows; r0 += Y.logit_rows) {
+        const int m = n_rows - r0 < Y.logit_rows ? n_rows - r0 : Y.logit_rows;
+        memcpy(p->h_ids, rows + r0, (size_t)m * 4);
+        CK(cudaMemcpyAsync(Y.rows, p->h_ids, (size_t)m * 4, cudaMemcpyHostToDevice, p->stream));
+        ly::NormArgs a{};
+        a.x = Y.X; a.w_pre = Y.final_norm; a.gather = Y.rows; a.eps = Y.c.norm_eps; a.E = E;
+        a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
+        if ((rc = launch_k(p, false, ly::k_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
+        if ((rc = ly_project<ly::EPI_STORE>(p, false, m, Y.A32, Y.A16, Y.head, nullptr, V, E, Y.LOG, nullptr, V, 0))) return rc;
+        CK(cudaMemcpyAsync(logits_out + (size_t)r0 * V, Y.LOG, (size_t)m * V * 4, cudaMemcpyDeviceToHost, p->stream));
+        CK(cudaStreamSynchronize(p->stream));
+    }
+    if (trace_out)
+        for (size_t r = 0; r < Y.runs.size(); r++)
+            CK(cudaMemcpy(trace_out + r * (size_t)n * E, Y.trace + r * (size_t)Y.cap * E, (size_t)n * E * 4, cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
+static int ly_kv_reset(b200_plan *p) {
+    Layered &Y = *p->ly;
+    for (LyRun &R : Y.runs) {
+        const LyLayer &L = Y.layers[R.layer];
+        CK(cudaMemsetAsync(R.kc, 0, (size_t)Y.ring * L.kd * 4, p->stream));
+        CK(cudaMemsetAsync(R.vc, 0, (size_t)Y.ring * L.vd * 4, p->stream));
+    }
+    CK(cudaStreamSynchronize(p->stream));
+    return B200_OK;
+}
+
+// "x" (row 0 of the residual stream), "logits", "key_cache" / "value_cache" of RUN `layer` ([ring][kv width])
+static int ly_read_buffer(b200_plan *p, const char *name, int layer, void *dst, size_t bytes) {
+    Layered &Y = *p->ly;
+    const std::string s = name;
+    const void *src = nullptr;
+    size_t sz = 0;
+    if (s == "x") { src = Y.X; sz = (size_t)Y.c.width * 4; }
+    else if (s == "logits") { src = p->logits; sz = (size_t)Y.c.vocab_size * 4; }
+    else if (s == "key_cache" || s == "value_cache") {
+        if (layer < 0 || layer >= (int)Y.runs.size()) return fail(p, B200_ERR_BAD_ARG, "run out of range");
+        const LyLayer &L = Y.layers[Y.runs[layer].layer];
+        src = s == "key_cache" ? Y.runs[layer].kc : Y.runs[layer].vc;
+        sz = (size_t)Y.ring * (s == "key_cache" ? L.kd : L.vd) * 4;
+    } else return fail(p, B200_ERR_BAD_ARG, "unknown buffer %s", name);
+    if (bytes < sz) sz = bytes;
+    CK(cudaSetDevice(p->device));
+    CK(cudaStreamSynchronize(p->stream));
+    CK(cudaMemcpy(dst, src, sz, cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+
+// Stand-alone timing of one projection of the decode step, cycling over the layers so the weights are not L2-resident:
+// which 0 = gated feed-forward projection, 1 = down projection, 2 = fused q|k|v|gate projection, 3 = output projection, 4 = classifier.
+static int ly_time_kernel(b200_plan *p, int which, int reps, float *avg_ms, int64_t *algorithmic_bytes) {
+    Layered &Y = *p->ly;
+    const int E = Y.c.width;
+    CK(cudaSetDevice(p->device));
+    CK(cudaStreamSynchronize(p->stream));
+    int launches = 0, rc;
+    int64_t bytes = 0;
+    auto one = [&](const LyLayer *L) -> int {
+        switch (which) {
+        case 0: if (!L->w_gu) return B200_OK; bytes = (int64_t)2 * L->s.ff_dim * E * 2; launches++;
+                return ly_project<ly::EPI_GATED>(p, true, 1, Y.A32, nullptr, L->w_gu, nullptr, L->s.ff_dim, E, Y.H32, nullptr, L->s.ff_dim, L->s.ff_act);
+        case 1: if (!L->w_down) return B200_OK; bytes = (int64_t)L->s.ff_dim * E * 2; launches++;
+                return ly_project<ly::EPI_STORE>(p, true, 1, Y.H32, nullptr, L->w_down, nullptr, E, L->s.ff_dim, Y.Y, nullptr, E, 0);
+        case 2: bytes = (int64_t)L->P * E * 2; launches++;
+                return ly_project<ly::EPI_STORE>(p, true, 1, Y.A32, nullptr, L->w_proj, L->b_proj, L->P, E, Y.PROJ, nullptr, Y.maxP, 0);
+        case 3: bytes = (int64_t)L->gd * E * 2; launches++;
+                return ly_project<ly::EPI_STORE>(p, true, 1, Y.ATT32, nullptr, L->w_o, nullptr, E, L->gd, Y.Y, nullptr, E, 0);
+        default: bytes = (int64_t)Y.c.vocab_size * E * 2; launches++;
+                return ly_project<ly::EPI_STORE>(p, true, 1, Y.A32, nullptr, Y.head, nullptr, Y.c.vocab_size, E, p->logits, nullptr, Y.c.vocab_size, 0);
+        }
+    };
+    if (which < 0 || which > 4) return fail(p, B200_ERR_BAD_ARG, "which must be 0..4");
+    for (const LyLayer &L : Y.layers) if ((rc = one(&L))) return rc; // warm-up pass
+    launches = 0;
+    CK(cudaEventRecord(p->ev0, p->stream));
+    for (int r = 0; r < reps; r++)
+        for (const LyLayer &L : Y.layers) { if ((rc = one(&L))) return rc; if (which == 4) break; }
+    CK(cudaEventRecord(p->ev1, p->stream));
+    CK(cudaStreamSynchronize(p->stream));
+    float ms = 0.f;
+    CK(cudaEventElapsedTime(&ms, p->ev0, p->ev1));
+    if (launches == 0) return fail(p, B200_ERR_UNSUPPORTED, "the plan has no such projection");
+    *avg_ms = ms / launches;
+    if (algorithmic_bytes) *algorithmic_bytes = bytes;
+    return B200_OK;
+}

@@ -55,8 +55,11 @@ struct Uploader {
     int64_t h2d_bytes = 0;
 };
 
+struct Layered; // layered_plan.cuh: models given as a list of layer specifications (b200_plan_create_layered)
+
 struct b200_plan {
     b200_config cfg{};
+    Layered *ly = nullptr; // set for layered plans; the shared entry points dispatch on it
     Uploader up;
     int device = 0;
     int wtype = 0; // B200_GGML_Q8_0 or B200_GGML_F16 (matrix type)
@@ -1344,7 +1347,46 @@ int check_pos(b200_plan *p, int token, int pos) {
 
 } // namespace
 
+#include "layered_plan.cuh"
+
 extern "C" {
+
+int b200_plan_create_layered(const b200_layered_config *cfg, const b200_layer_spec *layers, const b200_tensor *tensors, int32_t n_tensors,
+                             int32_t prefill_batch_size, int32_t device, b200_plan **out, char *err, size_t err_len) {
+    if (out) *out = nullptr;
+    if (!cfg || !layers || !tensors || !out || n_tensors <= 0) {
+        if (err && err_len) snprintf(err, err_len, "null argument");
+        return B200_ERR_BAD_ARG;
+    }
+    b200_plan *p = new b200_plan();
+    p->device = device;
+    p->prefill_batch = prefill_batch_size;
+    int rc = ly_build(p, cfg, layers, tensors, n_tensors);
+    if (rc != B200_OK) {
+        if (err && err_len) snprintf(err, err_len, "%s", p->err.c_str());
+        b200_plan_free(p);
+        return rc;
+    }
+    *out = p;
+    return B200_OK;
+}
+
+int b200_forward_batch_logits(b200_plan *p, const int32_t *tokens, int32_t n, int32_t start_pos, const int32_t *rows, int32_t n_rows, float *logits,
+                              float *residual_trace) {
+    if (!p || !tokens || n <= 0 || n_rows < 0) return B200_ERR_BAD_ARG;
+    if (!p->ly) return fail(p, B200_ERR_UNSUPPORTED, "logits of prefill rows are computed by layered plans only (GGUF plans prefill without logits, as the reference does)");
+    CK(cudaSetDevice(p->device));
+    return ly_batch(p, tokens, n, start_pos, rows, n_rows, logits, residual_trace);
+}
+
+int b200_layered_info(b200_plan *p, int32_t *runs, int32_t *ring_slots, int32_t *chunk_rows, int32_t *compute) {
+    if (!p || !p->ly) return B200_ERR_BAD_ARG;
+    if (runs) *runs = (int32_t)p->ly->runs.size();
+    if (ring_slots) *ring_slots = p->ly->ring;
+    if (chunk_rows) *chunk_rows = p->ly->cap;
+    if (compute) *compute = p->ly->c.compute;
+    return B200_OK;
+}
 
 int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t n_tensors, int32_t prefill_batch_size,
                      int32_t device, b200_plan **out, char *err, size_t err_len) {
@@ -1434,6 +1476,7 @@ int b200_forward_batch_prefill(b200_plan *p, const int32_t *tokens, int32_t n, i
     for (int i = 0; i < n; i++)
         if (tokens[i] < 0 || tokens[i] >= p->cfg.vocab_size) return fail(p, B200_ERR_BAD_ARG, "token %d out of range", tokens[i]);
     CK(cudaSetDevice(p->device));
+    if (p->ly) return ly_batch(p, tokens, n, start_pos, nullptr, 0, nullptr, nullptr);
     if (p->prefill.ready && p->prefill.mode == 1) { // tensor-core GEMM path (prefill.cuh)
         memcpy(p->h_ids, tokens, (size_t)n * 4);
         CK(cudaMemcpyAsync(p->prefill.tok, p->h_ids, (size_t)n * 4, cudaMemcpyHostToDevice, p->stream));
@@ -1545,6 +1588,7 @@ int b200_prefill_info(b200_plan *p, int32_t *mode, int32_t *launches, float *dev
 int b200_kv_reset(b200_plan *p) {
     if (!p) return B200_ERR_BAD_ARG;
     CK(cudaSetDevice(p->device));
+    if (p->ly) return ly_kv_reset(p);
     size_t kv_bytes = (size_t)p->cfg.n_layers * p->cfg.context_length * p->kvd_l * 4;
     CK(cudaMemsetAsync(p->key_cache, 0, kv_bytes, p->stream));
     CK(cudaMemsetAsync(p->value_cache, 0, kv_bytes, p->stream));
@@ -1554,6 +1598,7 @@ int b200_kv_reset(b200_plan *p) {
 
 int b200_read_buffer(b200_plan *p, const char *name, int32_t layer, void *dst, size_t bytes) {
     if (!p || !name || !dst) return B200_ERR_BAD_ARG;
+    if (p->ly) return ly_read_buffer(p, name, layer, dst, bytes);
     const b200_config &c = p->cfg;
     const void *src = nullptr;
     size_t sz = 0;
@@ -1583,6 +1628,7 @@ int b200_read_buffer(b200_plan *p, const char *name, int32_t layer, void *dst, s
 int b200_time_kernel(b200_plan *p, int32_t which, int32_t reps, float *avg_ms, int64_t *algorithmic_bytes) {
     if (!p || !avg_ms || reps <= 0) return B200_ERR_BAD_ARG;
     if (p->cfg.tp_size > 1) return fail(p, B200_ERR_UNSUPPORTED, "b200_time_kernel is single-GPU only");
+    if (p->ly) return ly_time_kernel(p, which, reps, avg_ms, algorithmic_bytes);
     const b200_config &c = p->cfg;
     const bool q8 = p->wtype == B200_GGML_Q8_0;
     CK(cudaSetDevice(p->device));
@@ -1735,6 +1781,7 @@ int b200_trace_decode(b200_plan *p, int32_t token, int32_t position, uint64_t *r
 
 int b200_profile_norm(b200_plan *p, int64_t *cycles4) {
     if (!p || !cycles4) return B200_ERR_BAD_ARG;
+    if (p->ly) return fail(p, B200_ERR_UNSUPPORTED, "the norm profile belongs to the exact sequential-sum kernel of GGUF plans");
     CK(cudaSetDevice(p->device));
     long long *d = nullptr;
     CK(cudaMalloc(&d, 128));
@@ -1862,6 +1909,7 @@ void b200_plan_free(b200_plan *p) {
     if (!p) return;
     cudaSetDevice(p->device);
     if (p->stream) cudaStreamSynchronize(p->stream);
+    ly_free(p);
     prefill_free(p->prefill);
     if (p->g_decode) cudaGraphExecDestroy(p->g_decode);
     if (p->g_prefill) cudaGraphExecDestroy(p->g_prefill);

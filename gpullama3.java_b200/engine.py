@@ -95,3 +95,32 @@ def generate_tokens_llama_batch_prefill(plan, latest_token: int, start_position:
         current = nxt
         pos += 1
     return generated
+
+
+def generate_tokens_layered(plan, prompt_tokens: list[int], stop_tokens: Iterable[int], max_tokens: int, context_length: int,
+                            batch_size: int, sampler=None, start_position: int = 0) -> list[int]:
+    """Generation loop of layered plans (positions count from 0, no begin-of-text convention): the prompt but its last token goes
+    through the batched prefill in chunks of at most ``batch_size`` tokens, then single-token decode steps from the last prompt
+    token on -- the chunk / decode split of generate_tokens_llama_batch_prefill.  ``sampler`` is a sampler.Sampler (device-side
+    temperature / top-p); None samples greedily."""
+    if max_tokens < 0 or context_length < max_tokens:
+        max_tokens = context_length
+    n = len(prompt_tokens)
+    if n == 0:
+        raise IndexError("empty prompt")
+    stop = set(stop_tokens)
+    pos = start_position
+    while pos - start_position < n - 1 and pos < max_tokens:
+        m = min(batch_size, n - 1 - (pos - start_position), max_tokens - pos)
+        plan.forward_batch_prefill(prompt_tokens[pos - start_position:pos - start_position + m], pos)
+        pos += m
+    generated: list[int] = []
+    current = prompt_tokens[n - 1]
+    while pos < max_tokens:
+        nxt = sampler.sample_token(plan, current, pos) if sampler is not None else plan.forward_decode(current, pos, logits=False)[1]
+        generated.append(nxt)
+        if nxt in stop:
+            break
+        current = nxt
+        pos += 1
+    return generated

@@ -11,11 +11,20 @@ from dataclasses import dataclass
 
 import numpy as np
 
+import json
+import os
+from dataclasses import field
+
 from .gguf import GGMLType, GGUFFile
+from .safetensors import SafetensorsFile
 
 ARCH_LLAMA = 0
 ARCH_QWEN3 = 1
 ARCH_PHI3 = 2
+ARCH_PIBIDRA = 3
+
+GGML_BF16 = 30  # ggml's id for bfloat16; layered plans take their safetensors tensors under it
+_SAFETENSORS_TYPES = {"BF16": GGML_BF16, "F16": GGMLType.F16, "F32": GGMLType.F32}
 
 
 @dataclass
@@ -40,6 +49,54 @@ class Configuration:
     @property
     def kv_dim(self):
         return self.n_kv_heads * self.head_size
+
+
+@dataclass
+class LayerSpec:
+    """One layer of a layered model (``b200_layer_spec``): a windowed attention mixer and an optional gated feed-forward."""
+    heads: int
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    window: int
+    bias_rows: int      # rows of the learned distance table (0: none)
+    bias_far: float     # largest distance the logarithmic rows resolve
+    score_scale: float
+    softcap: float
+    sink: bool = True
+    gate: bool = True
+    qkv_bias: bool = True
+    qk_norm: bool = True
+    ff_dim: int = 0     # 0: no feed-forward
+    ff_act: str = "gelu_tanh"
+    mixer: str = "window_attention"
+
+
+@dataclass
+class LayeredConfiguration:
+    """Configuration of a model given as a list of layers (``b200_layered_config``)."""
+    arch: int
+    width: int
+    vocab_size: int
+    context_length: int
+    norm_eps: float
+    embedding_scale: float
+    layers: list = field(default_factory=list)
+    loop: tuple | None = None  # (start, stop, times): layers [start, stop) run `times` passes over the same weights
+    quantization: str = "BF16"
+
+    @property
+    def n_layers(self):
+        return len(self.layers)
+
+    @property
+    def dim(self):
+        return self.width
+
+    def layer_runs(self) -> int:
+        if self.loop is None or self.loop[1] <= self.loop[0]:
+            return len(self.layers)
+        return len(self.layers) + (self.loop[2] - 1) * (self.loop[1] - self.loop[0])
 
 
 class UnsupportedModel(Exception):
@@ -95,8 +152,59 @@ def model_from_tensors(shape, quant: int, tensors: dict, context_length: int) ->
     return Model(None, cfg, {"llama": "LLAMA_3", "qwen3": "QWEN_3", "phi3": "PHI_3"}[shape.arch], tensors)
 
 
+def pibidra_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -> LayeredConfiguration:
+    """config.json of a Pibidra model -> LayeredConfiguration.  Every size comes from the file; the shape of each layer's
+    distance table gives its row count."""
+    layers = []
+    for i, lc in enumerate(cfg["layers"]):
+        if lc["type"] != "attention":
+            raise UnsupportedModel(f"layer {i}: mixer type {lc['type']!r} (Pibidra layers are 'attention')")
+        m, mlp = lc["mixer"], lc.get("mlp")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise UnsupportedModel(f"layer {i}: feed-forward kind {mlp.get('kind')!r}")
+        rel = tensor_shapes.get(f"l{i}.mix.rel")
+        if rel is None or len(rel) != 2 or rel[1] != int(m["heads"]):
+            raise UnsupportedModel(f"layer {i}: distance table l{i}.mix.rel missing or not [rows][heads]")
+        layers.append(LayerSpec(
+            heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), key_dim=int(m["dim"]), value_dim=int(m["vdim"]),
+            window=int(m["mask"]["size"]), bias_rows=int(rel[0]), bias_far=float(m["bias_max"]), score_scale=float(m["scale"]),
+            softcap=float(m["softcap"]), ff_dim=int(mlp["ff"]) if mlp is not None else 0))
+    loop = cfg.get("loop")
+    return LayeredConfiguration(
+        ARCH_PIBIDRA, int(cfg["width"]), int(cfg["vocab"]), int(context_length), float(cfg["norm"]["eps"]), float(cfg["embedding"]["scale"]),
+        layers, (int(loop["start"]), int(loop["stop"]), int(loop["times"])) if loop else None)
+
+
+# config.json "architecture" -> (model type, configuration builder): the registry of safetensors model directories
+CONFIG_ARCHITECTURES = {"Pibidra": ("PIBIDRA", pibidra_configuration)}
+DEFAULT_LAYERED_CONTEXT = 4096
+
+
+def load_model_dir(path: str, context_length: int = -1) -> Model:
+    """A directory with config.json + model.safetensors; the model class is chosen by config.json's "architecture"."""
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    arch = cfg.get("architecture")
+    if arch not in CONFIG_ARCHITECTURES:
+        raise UnsupportedModel(f"architecture {arch!r} is not one of {sorted(CONFIG_ARCHITECTURES)}")
+    typ, make = CONFIG_ARCHITECTURES[arch]
+    st = SafetensorsFile(os.path.join(path, "model.safetensors"))
+    tensors, shapes = {}, {}
+    for name, (dt, shape, _, _) in st.infos.items():
+        if dt not in _SAFETENSORS_TYPES:
+            raise UnsupportedModel(f"tensor {name}: dtype {dt}")
+        shapes[name] = shape
+        tensors[name] = (_SAFETENSORS_TYPES[dt], tuple(reversed(shape)), st.tensor_bytes(name))  # dims[0] = innermost, as in GGUF
+    config = make(cfg, shapes, DEFAULT_LAYERED_CONTEXT if context_length < 0 else context_length)
+    m = Model(None, config, typ, tensors)
+    m.safetensors = st
+    return m
+
+
 def load_model(path: str, context_length: int = -1) -> Model:
-    """``ModelLoader.loadModel(Path,int,boolean,boolean)`` (ModelLoader.java:113-120)."""
+    """``ModelLoader.loadModel(Path,int,boolean,boolean)`` (ModelLoader.java:113-120); a directory is a safetensors model."""
+    if os.path.isdir(path):
+        return load_model_dir(path, context_length)
     g = GGUFFile(path)
     md = g.metadata
     typ = detect_model_type(md)

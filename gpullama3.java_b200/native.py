@@ -34,12 +34,28 @@ class Config(C.Structure):
                 ("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
 
 
+class LayerSpec(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "key_dim", "value_dim", "window", "bias_rows")] + \
+               [(n, C.c_float) for n in ("bias_far", "score_scale", "softcap")] + \
+               [(n, C.c_int32) for n in ("sink", "gate", "qkv_bias", "qk_norm", "ff_kind", "ff_dim", "ff_act")]
+
+
+class LayeredConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("arch", "width", "vocab_size", "n_layers", "context_length")] + \
+               [("norm_eps", C.c_float), ("embedding_scale", C.c_float)] + \
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times", "compute")]
+
+
+COMPUTE_BF16, COMPUTE_F32 = 0, 1
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+
+
 class Tensor(C.Structure):
     _fields_ = [("name", C.c_char_p), ("data", C.c_void_p), ("ggml_type", C.c_int32), ("n_dims", C.c_int32),
                 ("dims", C.c_int64 * 4)]
 
 
-EXPORTS = ["b200_plan_create", "b200_forward_decode", "b200_forward_prefill", "b200_forward_batch_prefill", "b200_set_prefill_mode", "b200_prefill_info",
+EXPORTS = ["b200_plan_create_layered", "b200_forward_batch_logits", "b200_layered_info", "b200_plan_create", "b200_forward_decode", "b200_forward_prefill", "b200_forward_batch_prefill", "b200_set_prefill_mode", "b200_prefill_info",
            "b200_set_decode_mode", "b200_decode_info", "b200_trace_persistent", "b200_test_seqsum2", "b200_forward_decode_sample", "b200_upload_info", "b200_requant_kquant",
            "b200_decode_sequence", "b200_time_kernel", "b200_tp_handle", "b200_tp_attach", "b200_trace_decode", "b200_profile_norm", "b200_test_seqsum", "b200_gemm_f16", "b200_kv_reset", "b200_read_buffer", "b200_launches_per_decode",
            "b200_device_bytes", "b200_plan_free", "b200_last_error", "b200_version"]
@@ -57,6 +73,9 @@ def lib() -> C.CDLL:
     L = C.CDLL(LIB_PATH)
     vp, i32 = C.c_void_p, C.c_int32
     L.b200_plan_create.argtypes = [C.POINTER(Config), C.POINTER(Tensor), i32, i32, i32, C.POINTER(vp), C.c_char_p, C.c_size_t]
+    L.b200_plan_create_layered.argtypes = [C.POINTER(LayeredConfig), C.POINTER(LayerSpec), C.POINTER(Tensor), i32, i32, i32, C.POINTER(vp), C.c_char_p, C.c_size_t]
+    L.b200_forward_batch_logits.argtypes = [vp, vp, i32, i32, vp, i32, vp, vp]
+    L.b200_layered_info.argtypes = [vp, C.POINTER(i32), C.POINTER(i32), C.POINTER(i32), C.POINTER(i32)]
     L.b200_forward_decode.argtypes = [vp, i32, i32, vp, C.POINTER(i32)]
     L.b200_forward_prefill.argtypes = [vp, i32, i32]
     L.b200_forward_decode_sample.argtypes = [vp, i32, i32, C.c_float, C.c_float, C.c_float, C.POINTER(i32), C.POINTER(i32)]
@@ -137,13 +156,14 @@ def gemm_f16(a, b, iters: int = 0):
     return c, (ms.value if iters > 0 else None)
 
 
-GGML_SIZES = {0: (4, 1), 1: (2, 1), 8: (34, 32), 12: (144, 256), 13: (176, 256), 14: (210, 256)}  # (bytes, elements) per block, GGMLType.java:5-20
+GGML_SIZES = {30: (2, 1), 0: (4, 1), 1: (2, 1), 8: (34, 32), 12: (144, 256), 13: (176, 256), 14: (210, 256)}  # (bytes, elements) per block, GGMLType.java:5-20
 
 
 class NativePlan:
     """Owns one ``b200_plan*``."""
 
-    def __init__(self, cfg: Config, tensors: dict, prefill_batch_size: int = 0, device: int = 0):
+    def __init__(self, cfg, tensors: dict, prefill_batch_size: int = 0, device: int = 0, layer_specs=None):
+        """``cfg`` is a ``Config`` (GGUF plan) or a ``LayeredConfig`` with its ``layer_specs`` (layered plan)."""
         L = lib()
         arr = (Tensor * len(tensors))()
         self._keep = []
@@ -163,7 +183,12 @@ class NativePlan:
                 arr[i].dims[k] = int(d)
         out = C.c_void_p()
         err = C.create_string_buffer(512)
-        rc = L.b200_plan_create(C.byref(cfg), arr, len(tensors), prefill_batch_size, device, C.byref(out), err, 512)
+        self.layered = layer_specs is not None
+        if self.layered:
+            specs = (LayerSpec * len(layer_specs))(*layer_specs)
+            rc = L.b200_plan_create_layered(C.byref(cfg), specs, arr, len(tensors), prefill_batch_size, device, C.byref(out), err, 512)
+        else:
+            rc = L.b200_plan_create(C.byref(cfg), arr, len(tensors), prefill_batch_size, device, C.byref(out), err, 512)
         self._keep = None  # the library never touches the host pointers again
         if rc != B200_OK:
             _raise(rc, err.value.decode())
@@ -218,6 +243,24 @@ class NativePlan:
     def forward_batch_prefill(self, tokens, start_pos: int):
         t = np.ascontiguousarray(tokens, dtype=np.int32)
         self._ck(lib().b200_forward_batch_prefill(self._p, t.ctypes.data, len(t), start_pos))
+
+    def forward_batch_logits(self, tokens, start_pos: int, rows=(), want_trace: bool = False):
+        """One prefill chunk; returns (logits [len(rows), vocab] of the chosen chunk rows, residual stream after every layer run or None)."""
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        r = np.ascontiguousarray(rows, dtype=np.int32)
+        out = np.empty((len(r), self.cfg.vocab_size), dtype=np.float32)
+        trace = None
+        if want_trace:
+            trace = np.empty((self.layered_info()[0], len(t), self.cfg.width), dtype=np.float32)
+        self._ck(lib().b200_forward_batch_logits(self._p, t.ctypes.data, len(t), start_pos, r.ctypes.data if len(r) else None, len(r),
+                                                 out.ctypes.data if len(r) else None, trace.ctypes.data if want_trace else None))
+        return out, trace
+
+    def layered_info(self):
+        """(layer runs, cache slots per run, rows per chunk, compute mode) of a layered plan."""
+        a, b, c, d = C.c_int32(0), C.c_int32(0), C.c_int32(0), C.c_int32(0)
+        self._ck(lib().b200_layered_info(self._p, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+        return a.value, b.value, c.value, d.value
 
     def decode_sequence(self, tokens, n: int, start_pos: int, feedback: bool = False):
         t = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -57,6 +57,28 @@ def exchange_handles(handle: bytes, group=None) -> list[bytes]:
     return out
 
 
+def make_layered_config(model: Model, compute: str = "bfloat16"):
+    """LayeredConfiguration -> (b200_layered_config, [b200_layer_spec])."""
+    c = model.configuration
+    cfg = native.LayeredConfig()
+    cfg.arch, cfg.width, cfg.vocab_size, cfg.n_layers, cfg.context_length = c.arch, c.width, c.vocab_size, c.n_layers, c.context_length
+    cfg.norm_eps, cfg.embedding_scale = c.norm_eps, c.embedding_scale
+    cfg.loop_start, cfg.loop_stop, cfg.loop_times = c.loop if c.loop is not None else (0, 0, -1)
+    cfg.compute = {"bfloat16": native.COMPUTE_BF16, "bf16": native.COMPUTE_BF16, "float32": native.COMPUTE_F32, "f32": native.COMPUTE_F32}[compute]
+    specs = []
+    for s in c.layers:
+        if s.mixer != "window_attention":
+            raise native.UnsupportedOperation(-2, f"mixer {s.mixer!r}")
+        sp = native.LayerSpec()
+        sp.mixer = 1
+        sp.heads, sp.kv_heads, sp.key_dim, sp.value_dim, sp.window = s.heads, s.kv_heads, s.key_dim, s.value_dim, s.window
+        sp.bias_rows, sp.bias_far, sp.score_scale, sp.softcap = s.bias_rows, s.bias_far, s.score_scale, s.softcap
+        sp.sink, sp.gate, sp.qkv_bias, sp.qk_norm = int(s.sink), int(s.gate), int(s.qkv_bias), int(s.qk_norm)
+        sp.ff_kind, sp.ff_dim, sp.ff_act = (1 if s.ff_dim > 0 else 0), s.ff_dim, native.ACTIVATIONS[s.ff_act]
+        specs.append(sp)
+    return cfg, specs
+
+
 def make_config(model: Model, fp16_lanes: int | None = None) -> native.Config:
     c = model.configuration
     cfg = native.Config()
@@ -74,9 +96,17 @@ class B200MasterPlan:
     """One plan per model, used from one thread at a time (InferenceService.java:31,58)."""
 
     def __init__(self, model: Model, prefill_batch_size: int | None = None, device: int = 0, fp16_lanes: int | None = None,
-                 tp_rank: int = 0, tp_size: int = 1, tp_group=None):
+                 tp_rank: int = 0, tp_size: int = 1, tp_group=None, compute: str = "bfloat16"):
         self.model = model
         self.prefill_batch_size = PREFILL_BATCH_SIZE if prefill_batch_size is None else prefill_batch_size
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        self.layered = hasattr(model.configuration, "layers")
+        if self.layered:  # a list of layer specifications (safetensors model directory); ``compute`` = "bfloat16" | "float32"
+            if tp_size > 1:
+                raise native.UnsupportedOperation(-2, "layered plans are single-GPU")
+            cfg, specs = make_layered_config(model, compute)
+            self._native = native.NativePlan(cfg, model.tensors, max(1, self.prefill_batch_size), device, layer_specs=specs)
+            return
         cfg = make_config(model, fp16_lanes)
         cfg.tp_rank, cfg.tp_size = tp_rank, tp_size
         if tp_size > 1:
@@ -115,6 +145,14 @@ class B200MasterPlan:
     # void tornadoVMForwardBatchPrefill()  (TornadoVMMasterPlanBatchPrefillDecode.java:107-123)
     def forward_batch_prefill(self, tokens, start_pos: int):
         self._native.forward_batch_prefill(np.asarray(tokens, dtype=np.int32), start_pos)
+
+    def forward_batch_logits(self, tokens, start_pos: int, rows=(), want_trace: bool = False):
+        """Layered plans: one prefill chunk (at most ``prefill_batch_size`` tokens) that also returns the logits of the chunk
+        rows ``rows`` -- (logits [len(rows), vocab], residual stream after every layer run or None)."""
+        return self._native.forward_batch_logits(tokens, start_pos, rows, want_trace)
+
+    def layered_info(self):
+        return self._native.layered_info()
 
     # TensorCoreSupport.java's switch between the MMA and the plain batch-prefill layer families
     PREFILL_EXACT, PREFILL_TENSOR_CORE = 0, 1

@@ -40,10 +40,15 @@ extern "C" {
 #define B200_ARCH_PHI3 2  /* InferenceCore.forwardJavaPhi3,  InferenceCore.java:699-800: fused blk.N.attn_qkv.weight ([q; k; v] rows) and
                            * blk.N.ffn_up.weight ([gate; up] rows), NeoX-pair RoPE without q/k norm; n_heads * head_size == dim */
 
+#define B200_ARCH_PIBIDRA 3 /* a layered design (b200_plan_create_layered): sliding-window attention with a value-less softmax sink, a soft
+                             * logit cap and a learned bucketed distance bias, whole-projection q/k norm, sigmoid output gate, sandwich
+                             * norms, a gated GELU feed-forward and a block of layers that is run several times over the same weights */
+
 /* GGML tensor type ids accepted for weights (tensor/GGMLType.java:5-20) */
 #define B200_GGML_F32 0
 #define B200_GGML_F16 1
 #define B200_GGML_Q8_0 8
+#define B200_GGML_BF16 30 /* layered plans: matrices, vectors and tables as stored in a safetensors file */
 /* K-quants are accepted for weight matrices and the embedding table of a Q8_0 plan: they are re-quantised to Q8_0 on the device while
  * the upload pipeline streams them in, byte-identical to ModelLoader.dequantizeToQ8_0TornadoTensor (model/loader/ModelLoader.java:163,
  * 173-224); the plan then computes exactly as for a Q8_0 file (AbstractModelLoader.java:45-59). */
@@ -92,6 +97,66 @@ typedef struct b200_plan b200_plan;
  * On failure *out is NULL and err (if non-NULL) receives the message. */
 int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t n_tensors,
                      int32_t prefill_batch_size, int32_t device, b200_plan **out, char *err, size_t err_len);
+
+/* ---- layered plans ---------------------------------------------------------------------------------------------------
+ * A model given as a LIST of layers, each with its own mixer sizes and feed-forward, BF16 weights named as in the model's
+ * safetensors file (linear weights [out][in]; dims[0] is the innermost dimension, as for GGUF tensors) and an FP32 residual
+ * stream.  The plan answers the same forward entry points as a GGUF plan (b200_forward_decode, _decode_sample, _prefill,
+ * _batch_prefill, b200_decode_sequence, b200_kv_reset, b200_read_buffer) plus b200_forward_batch_logits.  Nothing of this
+ * exists in the reference. */
+#define B200_MIXER_WINDOW_ATTENTION 1
+#define B200_FF_NONE 0
+#define B200_FF_DENSE_GATED 1 /* down(act(gate x) * (up x)) */
+#define B200_ACT_GELU_TANH 0
+#define B200_ACT_SILU 1
+#define B200_COMPUTE_BF16 0 /* prefill GEMM operands rounded to BF16, FP32 accumulation; decode FP32 activations x BF16 weights */
+#define B200_COMPUTE_F32 1  /* every product in true FP32 (BF16 weights widen exactly) */
+
+typedef struct b200_layer_spec {
+    int32_t mixer;      /* B200_MIXER_* */
+    int32_t heads;      /* query heads */
+    int32_t kv_heads;   /* key/value heads; query head h reads key/value head h / (heads / kv_heads) */
+    int32_t key_dim;    /* per-head query/key size */
+    int32_t value_dim;  /* per-head value size */
+    int32_t window;     /* position i sees j with 0 <= i - j < window */
+    int32_t bias_rows;  /* rows of the learned distance table [bias_rows][heads] ("<layer>.mix.rel"); 0 = no distance bias.
+                           row(n) = n below bias_rows / 2, logarithmic up to bias_far, the last row beyond */
+    float bias_far;
+    float score_scale;  /* multiplies <q, k> (not the bias) */
+    float softcap;      /* score <- softcap * tanh(score / softcap); <= 0: none */
+    int32_t sink;       /* 1: softmax denominator 1 + sum exp (an extra zero logit without a value) */
+    int32_t gate;       /* 1: heads * sigmoid(W_g h) before the output projection ("<layer>.mix.g") */
+    int32_t qkv_bias;   /* 1: "<layer>.mix.{q,k,v}.b" */
+    int32_t qk_norm;    /* 1: one RMS norm over the whole q projection and one over the whole k projection, weights used as stored */
+    int32_t ff_kind;    /* B200_FF_* */
+    int32_t ff_dim;
+    int32_t ff_act;     /* B200_ACT_* */
+} b200_layer_spec;
+
+typedef struct b200_layered_config {
+    int32_t arch;           /* B200_ARCH_PIBIDRA */
+    int32_t width;
+    int32_t vocab_size;
+    int32_t n_layers;
+    int32_t context_length; /* highest position + 1 the plan accepts; cache memory is bounded by the windows, not by this */
+    float norm_eps;
+    float embedding_scale;
+    int32_t loop_start, loop_stop, loop_times; /* layers [loop_start, loop_stop) run loop_times passes; loop_times < 0: no loop */
+    int32_t compute;        /* B200_COMPUTE_* */
+} b200_layered_config;
+
+/* prefill_batch_size = the most tokens one b200_forward_batch_prefill / _batch_logits call takes (>= 1). */
+int b200_plan_create_layered(const b200_layered_config *cfg, const b200_layer_spec *layers, const b200_tensor *tensors, int32_t n_tensors,
+                             int32_t prefill_batch_size, int32_t device, b200_plan **out, char *err, size_t err_len);
+
+/* One chunk of n tokens at positions start_pos.. through the batched prefill kernels, like b200_forward_batch_prefill, and
+ * additionally the logits of the chunk rows rows[0..n_rows) into logits ([n_rows][vocab_size], host).  residual_trace
+ * (nullable, host, [layer runs][n][width]) receives the residual stream after every layer run (a diagnostic). */
+int b200_forward_batch_logits(b200_plan *plan, const int32_t *tokens, int32_t n, int32_t start_pos, const int32_t *rows, int32_t n_rows, float *logits,
+                              float *residual_trace);
+
+/* Layer runs (a looped layer counts once per pass), cache slots per run, rows per chunk, compute mode. */
+int b200_layered_info(b200_plan *plan, int32_t *runs, int32_t *ring_slots, int32_t *chunk_rows, int32_t *compute);
 
 /* TornadoVMMasterPlan.tornadoVMForwardDecode(position) with the embedding gather moved
  * device-side (replaces InferenceCore.forwardTornadoVM, InferenceCore.java:956-980, which copies
