@@ -393,3 +393,78 @@ def build_tensors_fast(shape: Shape, quant: int, seed: int = 1234, device: str |
         assert ho == nbytes
         out[name] = (tt, dims, host)
     return out
+
+
+# ---- Pibidra: seeded synthetic model directories (config.json + model.safetensors) ----------------------------------------
+def pibidra_layer(heads: int, kv_heads: int, key_dim: int, value_dim: int, window: int, ff: int | None, scale: float | None = None,
+                  softcap: float = 30.0, bias_max: float = 64.0) -> dict:
+    """One entry of config.json's "layers" (ff = None: a layer without feed-forward)."""
+    return {"type": "attention",
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": key_dim, "vdim": value_dim, "mask": {"size": window},
+                      "scale": float(key_dim ** -0.5 if scale is None else scale), "softcap": float(softcap), "bias_max": float(bias_max)},
+            "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def pibidra_config(width: int, vocab: int, layers: list, loop: tuple | None = None, eps: float = 1e-6, embedding_scale: float = 8.0) -> dict:
+    cfg = {"architecture": "Pibidra", "width": width, "vocab": vocab, "embedding": {"scale": float(embedding_scale)}, "norm": {"eps": float(eps)},
+           "layers": layers}
+    if loop is not None:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def pibidra_weights(cfg: dict, seed: int = 0, bias_rows: int = 8) -> dict:
+    """name -> float32 array in the shapes the loader expects (linear weights [out][in]); values are BF16-representable."""
+    from .safetensors import bf16_bits, bf16_to_f32
+
+    rng = np.random.default_rng(seed)
+    E, V = cfg["width"], cfg["vocab"]
+    w = {}
+
+    def mat(o, i, gain=1.0):
+        return (rng.standard_normal((o, i)) * gain / np.sqrt(i)).astype(np.float32)
+
+    w["embed"] = (rng.standard_normal((V, E)) * 0.1).astype(np.float32)
+    w["head"] = mat(V, E)
+    w["final.norm"] = (0.2 * rng.standard_normal(E)).astype(np.float32)
+    if "loop" in cfg:
+        w["loop.step"] = (0.3 * rng.standard_normal((cfg["loop"]["times"], E))).astype(np.float32)
+    for i, lc in enumerate(cfg["layers"]):
+        m, p = lc["mixer"], f"l{i}."
+        H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        for n in ("norm1", "norm1b") + (("norm2", "norm2b") if lc["mlp"] is not None else ()):
+            w[p + n] = (0.2 * rng.standard_normal(E)).astype(np.float32)
+        w[p + "mix.q"], w[p + "mix.q.b"] = mat(H * dk, E, 2.0), (0.2 * rng.standard_normal(H * dk)).astype(np.float32)
+        w[p + "mix.k"], w[p + "mix.k.b"] = mat(G * dk, E, 2.0), (0.2 * rng.standard_normal(G * dk)).astype(np.float32)
+        w[p + "mix.v"], w[p + "mix.v.b"] = mat(G * dv, E), (0.2 * rng.standard_normal(G * dv)).astype(np.float32)
+        w[p + "mix.q.norm"] = (1.0 + 0.3 * rng.standard_normal(H * dk)).astype(np.float32)
+        w[p + "mix.k.norm"] = (1.0 + 0.3 * rng.standard_normal(G * dk)).astype(np.float32)
+        w[p + "mix.rel"] = rng.standard_normal((bias_rows, H)).astype(np.float32)
+        w[p + "mix.g"] = mat(H * dv, E)
+        w[p + "mix.o"] = mat(E, H * dv)
+        if lc["mlp"] is not None:
+            F = lc["mlp"]["ff"]
+            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = mat(F, E), mat(F, E), mat(E, F)
+    return {k: bf16_to_f32(bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+
+
+def write_pibidra_dir(path: str, cfg: dict, weights: dict) -> None:
+    import json
+    import os
+
+    from .safetensors import bf16_bits, write_safetensors
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f, indent=1)
+    write_safetensors(os.path.join(path, "model.safetensors"), {k: ("BF16", v.shape, bf16_bits(v)) for k, v in weights.items()})
+
+
+def pibidra_model(cfg: dict, weights: dict, context_length: int):
+    """In-memory loader.Model (benchmarks: synthetic weights never touch the disk)."""
+    from . import loader
+    from .safetensors import bf16_bits
+
+    tensors = {k: (loader.GGML_BF16, tuple(reversed(v.shape)), bf16_bits(v).view(np.uint8).reshape(-1)) for k, v in weights.items()}
+    config = loader.pibidra_configuration(cfg, {k: v.shape for k, v in weights.items()}, context_length)
+    return loader.Model(None, config, "PIBIDRA", tensors)

@@ -129,7 +129,7 @@ def layer_runs(cfg) -> list:
     """(layer index, pass number or None, first-of-pass) in execution order."""
     n = len(cfg["layers"])
     loop = cfg.get("loop")
-    if not loop or loop["times"] < 1 or loop["stop"] <= loop["start"]:
+    if not loop or loop["stop"] <= loop["start"]:
         return [(i, None, False) for i in range(n)]
     runs = [(i, None, False) for i in range(loop["start"])]
     for t in range(loop["times"]):
