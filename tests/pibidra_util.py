@@ -20,6 +20,16 @@ def oracle():
     return mod
 
 
+def bf16_values(weights: dict) -> dict:
+    """Round every value to the nearest BF16 (ties to even): what the device will hold after the upload."""
+    out = {}
+    for k, v in weights.items():
+        u = np.ascontiguousarray(v, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        r = (((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint32) << 16).view(np.float32)
+        out[k] = r.reshape(v.shape)
+    return out
+
+
 def w64(weights: dict) -> dict:
     return {k: v.astype(np.float64) for k, v in weights.items()}
 
@@ -65,7 +75,7 @@ def needle_model(S, window: int, kv_heads: int = 1, seed: int = 3):
     w["l0.mix.k"][:, B] = np.tile(u, kv_heads)
     w["l0.mix.v"][:, B] += 3.0 * rng.standard_normal(kv_heads * dv).astype(np.float32)
     fill = [t for t in range(V) if t not in (A, B)]
-    return cfg, w, A, B, fill
+    return cfg, bf16_values(w), A, B, fill
 
 
 def rel_rms(got, ref):

@@ -8,7 +8,7 @@ moves the row by more than 10 %."""
 import numpy as np
 import pytest
 
-from pibidra_util import configs, needle_model, oracle, rel_rms, w64
+from pibidra_util import bf16_values, configs, needle_model, oracle, rel_rms, w64
 
 pytestmark = pytest.mark.gpu
 
@@ -146,7 +146,7 @@ def test_window_edges_with_a_planted_key(pkg, compute, kv_heads):
             if i:
                 prefill_all(plan, toks[:i], 8)
             lg = plan.forward_decode(toks[i], i)[0]
-            assert rel_rms(lg, ref[i]) <= TOL_DECODE, f"decoded query {i}, key at distance {dist}"
+            assert rel_rms(lg, ref[i]) <= TOL[compute], f"decoded query {i}, key at distance {dist}"  # the keys came from the prefill kernels
             # everything decoded
             for p, t in enumerate(toks):
                 lg = plan.forward_decode(t, p)[0]
@@ -180,6 +180,7 @@ def test_distance_rows_sink_and_cap_alone(pkg):
             w["l0.mix.rel"][:] = -30.0
         if case == "cap":
             w["l0.mix.q.norm"][:] = 6.0
+        w = bf16_values(w)
         ref_lg, ref_tr = O.forward(cfg, w64(w), toks, want_layers=True)
         plan = make_plan(pkg, cfg, w, batch=64, compute="float32")
         try:
@@ -236,11 +237,12 @@ def test_greedy_generation_through_the_engine(pkg):
         stop = want[4]
         got = pkg.engine.generate_tokens_layered(plan, prompt, stop_tokens=[stop], max_tokens=64, context_length=64, batch_size=5)
         assert got == want[:want.index(stop) + 1]
-        plan.forward_batch_prefill(prompt[:-1], 0) if len(prompt) - 1 <= 5 else [plan.forward_batch_prefill(prompt[c:min(c + 5, len(prompt) - 1)], c) for c in range(0, len(prompt) - 1, 5)]
+        for c in range(0, len(prompt) - 1, 5):
+            plan.forward_batch_prefill(prompt[c:min(c + 5, len(prompt) - 1)], c)
         ids, _ = plan.decode_sequence([prompt[-1]], 12, len(prompt) - 1, feedback=True)
         assert ids.tolist() == want
         sampler = pkg.sampler.select_sampler(cfg["vocab"], 0.0, 0.9, 1)
-        got = pkg.engine.generate_tokens_layered(plan, prompt, stop_tokens=[], max_tokens=len(prompt) + 3, context_length=64, batch_size=8 if False else 5, sampler=sampler)
+        got = pkg.engine.generate_tokens_layered(plan, prompt, stop_tokens=[], max_tokens=len(prompt) + 3, context_length=64, batch_size=5, sampler=sampler)
         assert got == want[:4]
     finally:
         plan.free()
