@@ -95,6 +95,88 @@ def prefill_leg(pkg, lb, local: int, n: int, reps: int):
                          "peak_source": src, "unit": "TFLOP/s", "frac": tf / burst, "flop_per_chunk": {"gemm": gemm, "attention": att}, "traffic": None}}
 
 
+# ---- --compare pibidra: the layered design beside the closest GGUF model at equal size -------------------------------------
+# Sizes that resemble real layers (random weights, a few layers): the decode step is a weight stream (HBM roofline), the
+# prefill chunk is GEMMs + window attention (tensor roofline).  The closest existing model is the FP16 Qwen3 plan (grouped
+# key/value heads, q/k norm, FP32 residual, FP32 KV cache) with the same width, feed-forward width, heads and layer count.
+COMPARE_SIZES = {
+    # name: (width, ff, heads, kv_heads, head size, vocab, layers, window)
+    "1b-like": (2048, 8192, 32, 8, 64, 32768, 4, 1024),
+    "8b-like": (4096, 14336, 32, 8, 128, 32768, 2, 2048),
+}
+
+
+def compare_layered(pkg, lb, local: int, steps: int, warmup: int, sizes):
+    hbm, hbm_src = peaks()
+    burst, sustained, t_src = tensor_peak()
+    S = pkg.synth
+    out = {}
+    for name in sizes:
+        E, F, H, G, hs, V, NL, Wn = COMPARE_SIZES[name]
+        depth, n_pp = 64, 512
+        ctx = max(depth + steps + warmup + 8, n_pp + 8)
+        toks = np.asarray(lb.synthetic_tokens(V, ctx), dtype=np.int32)
+        row = {}
+        # the new design: NL layers, the middle ones looped twice (so NL + (NL - 2) layer runs)
+        cfg = S.pibidra_config(E, V, [S.pibidra_layer(H, G, hs, hs, Wn, F, bias_max=float(Wn)) for _ in range(NL)],
+                               loop=(1, NL - 1, 2) if NL > 2 else None)
+        runs = NL + (NL - 2 if NL > 2 else 0)
+        w = S.pibidra_weights(cfg, 1234, bias_rows=32)
+        per_run = (2 * H * hs + 2 * G * hs) * E + H * hs * E + 3 * F * E  # q, o, k, v, gate + feed-forward weights of one run
+        for mode in ("bfloat16",):
+            plan = pkg.B200MasterPlan.initialize_plan(S.pibidra_model(cfg, w, ctx), prefill_batch_size=n_pp, device=local, compute=mode)
+            plan.decode_sequence(toks[:depth + warmup], depth + warmup, 0)
+            _, ms = plan.decode_sequence(toks[depth + warmup:depth + warmup + steps], steps, depth + warmup)
+            dbytes = 2 * (runs * per_run + V * E)
+            pp = []
+            for r in range(3 + 3):
+                plan.forward_batch_prefill(toks[:n_pp], 0)
+                if r >= 3:
+                    pp.append(plan.prefill_info()[2])
+            pp_ms = float(np.mean(pp))
+            flop = 2.0 * runs * per_run * n_pp + 4.0 * runs * H * hs * sum(min(i + 1, Wn) for i in range(n_pp))
+            kern = {}
+            for which, kn in ((0, "gate_up"), (1, "down"), (2, "qkvg"), (3, "attn_out"), (4, "classifier")):
+                kms, kb = plan.time_kernel(which, 5)
+                kern[kn] = {"us": kms * 1e3, "GB/s": kb / kms / 1e6, "frac_hbm": kb / kms / 1e6 / hbm}
+            row["pibidra_" + mode] = {
+                "decode_tok_s": steps / ms * 1e3, "decode_ms": ms / steps, "decode_frac_hbm": dbytes / (ms / steps * 1e-3) / 1e9 / hbm,
+                "launches_per_decode": plan.launches_per_decode, "layer_runs": runs,
+                "prefill_tok_s": n_pp / pp_ms * 1e3, "prefill_ms": pp_ms, "prefill_tflops": flop / pp_ms / 1e9, "prefill_frac_tensor": flop / pp_ms / 1e9 / burst,
+                "prefill_launches": plan.prefill_info()[1], "decode_kernels": kern}
+            plan.free()
+        # the closest existing model at equal size: Qwen3-shaped FP16 GGUF with `runs` layers
+        shape = S.Shape("qwen3", E, F, runs, H, G, hs, V, False, 1000000.0, 1e-6, ctx)
+        F16 = pkg.gguf.GGMLType.F16
+        model = pkg.loader.model_from_tensors(shape, F16, S.build_tensors_fast(shape, F16, seed=1234, device=f"cuda:{local}"), ctx)
+        plan = pkg.B200MasterPlan.initialize_plan(model, prefill_batch_size=n_pp, device=local)
+        plan.decode_sequence(toks[:depth + warmup], depth + warmup, 0)
+        _, ms = plan.decode_sequence(toks[depth + warmup:depth + warmup + steps], steps, depth + warmup)
+        dbytes = 2 * shape.matmul_elements()
+        pp = []
+        for r in range(3 + 3):
+            plan.forward_batch_prefill(toks[:n_pp], 0)
+            if r >= 3:
+                pp.append(plan.prefill_info()[2])
+        pp_ms = float(np.mean(pp))
+        flop = 2.0 * shape.matmul_elements_no_head() * n_pp + 4.0 * shape.q_dim * runs * (n_pp * (n_pp + 1) / 2.0)
+        kern = {}
+        for which, kn in ((0, "gate_up"), (1, "down"), (2, "qkv"), (3, "attn_out"), (4, "classifier")):
+            kms, kb = plan.time_kernel(which, 5)
+            kern[kn] = {"us": kms * 1e3, "GB/s": kb / kms / 1e6, "frac_hbm": kb / kms / 1e6 / hbm}
+        row["qwen3_f16"] = {
+            "decode_tok_s": steps / ms * 1e3, "decode_ms": ms / steps, "decode_frac_hbm": dbytes / (ms / steps * 1e-3) / 1e9 / hbm,
+            "launches_per_decode": plan.launches_per_decode, "layers": runs,
+            "prefill_tok_s": n_pp / pp_ms * 1e3, "prefill_ms": pp_ms, "prefill_tflops": flop / pp_ms / 1e9, "prefill_frac_tensor": flop / pp_ms / 1e9 / burst,
+            "prefill_mode": "tensor_core" if plan.prefill_info()[0] == 1 else "exact", "prefill_launches": plan.prefill_info()[1], "decode_kernels": kern}
+        plan.free()
+        row["config"] = {"width": E, "ff": F, "heads": H, "kv_heads": G, "head_size": hs, "vocab": V, "layers": NL, "layer_runs": runs, "window": Wn,
+                         "decode": f"tg{steps} from depth {depth + warmup}", "prefill": f"pp{n_pp} in one chunk from depth 0"}
+        out[name] = row
+    return {"metric": "layered_vs_closest_model", "unit": "tok/s", "data": "synthetic", "dtype": "bf16 weights (Pibidra) / f16 weights (Qwen3), f32 accumulate",
+            "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
+
+
 class ClockSampler:
     """nvidia-smi clocks/throttle reasons sampled DURING the timed region."""
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
@@ -210,8 +292,24 @@ def main():
     ap.add_argument("--depth", type=int, default=-1, help="LlamaBench -d: KV positions filled before the timed steps (default: the warm-up steps)")
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama-3-8b", "llama-3-70b", "llama-3.2-1b", "qwen3-4b"],
                     help="shape of the synthetic model (default: the BASELINE headline, Llama-3-8B; 70B is BASELINE config 5, meant for --gpus 2/4/8)")
+    ap.add_argument("--compare", default=None, choices=["pibidra"],
+                    help="instead of the headline workload: decode and prefill throughput of the layered design beside the closest GGUF model "
+                         "(FP16 Qwen3 plan) at equal sizes, with per-kernel rooflines; one JSON line")
+    ap.add_argument("--compare-sizes", default="1b-like,8b-like")
     args = ap.parse_args()
     K, W = args.steps, max(args.warmup, 3)
+    if args.compare:
+        import torch
+
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        pkg = ge.import_package()
+        sampler = ClockSampler(local)
+        sampler.start()
+        line = compare_layered(pkg, pkg.llama_bench, local, min(K, 64), W, args.compare_sizes.split(","))
+        line["clocks"] = sampler.stop()
+        print(json.dumps(line))
+        return 0
     WORKLOAD = args.workload
     QUANT = args.quant
     pretty = {"llama-3-8b": "Llama-3-8B", "llama-3-70b": "Llama-3-70B", "llama-3.2-1b": "Llama-3.2-1B", "qwen3-4b": "Qwen3-4B"}[WORKLOAD]

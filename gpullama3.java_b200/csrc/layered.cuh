@@ -355,14 +355,19 @@ struct WindowAttn {
 };
 // Row layout of the fused projection output: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv | g: heads*dv]
 
-// One CTA per row: RMS statistics over the WHOLE q and the WHOLE k projection, q normalised in place, k / v into the ring.
-__global__ void __launch_bounds__(256) k_qk_prep(float *__restrict__ P, int ldp, WindowAttn a, float *__restrict__ kc, float *__restrict__ vc,
-                                                 const StepState *__restrict__ st) {
+// One CTA per row: projection biases, RMS statistics over the WHOLE q and the WHOLE k projection, q normalised in place,
+// k / v into the ring.
+__global__ void __launch_bounds__(256) k_qk_prep(float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ bias, float *__restrict__ kc,
+                                                 float *__restrict__ vc, const StepState *__restrict__ st) {
     __shared__ float red[32];
     const int r = blockIdx.x, tid = threadIdx.x;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
     float *q = P + (size_t)r * ldp, *k = q + qd, *v = k + kd;
     const int slot = (st->pos + r) % a.ring;
+    if (bias) { // q | k | v biases of the fused projection, added where it is consumed
+        for (int i = tid; i < qd + kd + vd; i += 256) q[i] += bias[i];
+        __syncthreads();
+    }
     float qinv = 1.0f, kinv = 1.0f;
     if (a.qnorm) {
         float ss = 0.0f;
@@ -452,6 +457,183 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
             float o = acc * inv;
             if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d]));
             store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d, o);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The same attention for a prefill chunk on the tensor cores (BF16 compute mode): one CTA per (64 query rows, head), four
+// warps of 16 rows; key tiles of 64 positions are read from the FP32 ring, rounded to BF16 in shared memory (K as [key][d],
+// V transposed to [d][key]) and multiplied with mma.sync m16n8k16; scores, cap, distance bias, mask and the ONLINE softmax
+// stay in FP32 registers.  The sink is the initial state of the running softmax: maximum 0, denominator exp(0) = 1, no value.
+// Dynamic shared memory: att_mma_smem_bytes<DK, DV>(window).
+// ---------------------------------------------------------------------------------------------------------------------
+#define LY_ATT_MMA_THREADS 128
+template <int DK, int DV> __host__ __device__ constexpr size_t att_mma_smem_bytes(int window) {
+    return (size_t)(64 * (DK + 8) * 2) * 2 + (size_t)DV * (64 + 8) * 2 + (size_t)window * 4;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned *>(&v);
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(const float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ kc,
+                                                                             const float *__restrict__ vc, const StepState *__restrict__ st, int n,
+                                                                             bf16 *__restrict__ out, int ldo) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    bf16(*Qs)[DK + 8] = reinterpret_cast<bf16(*)[DK + 8]>(smraw);
+    bf16(*Ks)[DK + 8] = reinterpret_cast<bf16(*)[DK + 8]>(smraw + 64 * (DK + 8) * 2);
+    bf16(*Vt)[64 + 8] = reinterpret_cast<bf16(*)[64 + 8]>(smraw + 2 * 64 * (DK + 8) * 2);
+    float *sbias = reinterpret_cast<float *>(smraw + 2 * 64 * (DK + 8) * 2 + DV * (64 + 8) * 2);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int h = blockIdx.y, r0 = blockIdx.x * 64;
+    const int kd = a.kv_heads * DK, vd = a.kv_heads * DV, qd = a.heads * DK;
+    const int kvh = h / (a.heads / a.kv_heads);
+    const int pos0 = st->pos;
+    const int rows = n - r0 < 64 ? n - r0 : 64;
+    // distance -> bias of this head
+    for (int d = tid; d < a.window; d += LY_ATT_MMA_THREADS) sbias[d] = a.rel ? a.rel[(size_t)a.bucket[d] * a.heads + h] : 0.0f;
+    // Q tile -> BF16
+    for (int e = tid; e < 64 * (DK / 4); e += LY_ATT_MMA_THREADS) {
+        const int r = e / (DK / 4), c = (e % (DK / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows) v = *reinterpret_cast<const float4 *>(P + (size_t)(r0 + r) * ldp + (size_t)h * DK + c);
+        *reinterpret_cast<uint2 *>(&Qs[r][c]) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+    }
+    __syncthreads();
+    unsigned qf[DK / 16][4];
+    {
+        const int r = warp * 16 + g;
+#pragma unroll
+        for (int kk = 0; kk < DK / 16; kk++) {
+            qf[kk][0] = *reinterpret_cast<const unsigned *>(&Qs[r][kk * 16 + 2 * t]);
+            qf[kk][1] = *reinterpret_cast<const unsigned *>(&Qs[r + 8][kk * 16 + 2 * t]);
+            qf[kk][2] = *reinterpret_cast<const unsigned *>(&Qs[r][kk * 16 + 2 * t + 8]);
+            qf[kk][3] = *reinterpret_cast<const unsigned *>(&Qs[r + 8][kk * 16 + 2 * t + 8]);
+        }
+    }
+    float o[DV / 8][4];
+#pragma unroll
+    for (int j = 0; j < DV / 8; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[j][e] = 0.0f;
+    float mrow[2], lrow[2];
+    mrow[0] = mrow[1] = a.sink ? 0.0f : -INFINITY;
+    lrow[0] = lrow[1] = a.sink ? 1.0f : 0.0f;
+    const int prow[2] = {pos0 + r0 + warp * 16 + g, pos0 + r0 + warp * 16 + g + 8}; // positions of this thread's two rows
+    const bool vrow[2] = {warp * 16 + g < rows, warp * 16 + g + 8 < rows};
+    const int q_lo = pos0 + r0, q_hi = pos0 + r0 + rows - 1;
+    const int k_lo = q_lo - a.window + 1 > 0 ? q_lo - a.window + 1 : 0;
+    const float inv_cap = a.softcap > 0.0f ? 1.0f / a.softcap : 0.0f;
+    for (int kt0 = k_lo; kt0 <= q_hi; kt0 += 64) {
+        __syncthreads(); // the previous tile's fragments have been read
+        for (int e = tid; e < 64 * (DK / 4); e += LY_ATT_MMA_THREADS) {
+            const int r = e / (DK / 4), c = (e % (DK / 4)) * 4, p = kt0 + r;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p <= q_hi) v = *reinterpret_cast<const float4 *>(kc + (size_t)(p % a.ring) * kd + (size_t)kvh * DK + c);
+            *reinterpret_cast<uint2 *>(&Ks[r][c]) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+        }
+        for (int e = tid; e < 64 * (DV / 4); e += LY_ATT_MMA_THREADS) {
+            const int r = e / (DV / 4), c = (e % (DV / 4)) * 4, p = kt0 + r;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p <= q_hi) v = *reinterpret_cast<const float4 *>(vc + (size_t)(p % a.ring) * vd + (size_t)kvh * DV + c);
+            Vt[c][r] = __float2bfloat16_rn(v.x); Vt[c + 1][r] = __float2bfloat16_rn(v.y);
+            Vt[c + 2][r] = __float2bfloat16_rn(v.z); Vt[c + 3][r] = __float2bfloat16_rn(v.w);
+        }
+        __syncthreads();
+        // S = Q K^T for this warp's 16 rows x 64 keys
+        float sc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) sc[j][e] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < DK / 16; kk++) {
+                unsigned bfr[2];
+                bfr[0] = *reinterpret_cast<const unsigned *>(&Ks[j * 8 + g][kk * 16 + 2 * t]);
+                bfr[1] = *reinterpret_cast<const unsigned *>(&Ks[j * 8 + g][kk * 16 + 2 * t + 8]);
+                mma_bf16_16816(sc[j], qf[kk], bfr);
+            }
+        }
+        // cap, bias, mask; tile maximum per row
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int rr = e >> 1, pj = kt0 + j * 8 + 2 * t + (e & 1), dist = prow[rr] - pj;
+                float v = sc[j][e] * a.scale;
+                if (a.softcap > 0.0f) v = a.softcap * tanhf(v * inv_cap);
+                if (vrow[rr] && dist >= 0 && dist < a.window) v += sbias[dist];
+                else v = -INFINITY;
+                sc[j][e] = v;
+                tmax[rr] = fmaxf(tmax[rr], v);
+            }
+        float corr[2], muse[2];
+#pragma unroll
+        for (int rr = 0; rr < 2; rr++) {
+            tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
+            tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
+            const float mnew = fmaxf(mrow[rr], tmax[rr]);
+            muse[rr] = mnew == -INFINITY ? 0.0f : mnew;
+            corr[rr] = mrow[rr] == -INFINITY ? 0.0f : expf(mrow[rr] - muse[rr]);
+            mrow[rr] = mnew;
+            lrow[rr] *= corr[rr];
+        }
+        float psum[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float pv = expf(sc[j][e] - muse[e >> 1]); // exp(-inf) = 0 for masked entries
+                sc[j][e] = pv;
+                psum[e >> 1] += pv;
+            }
+#pragma unroll
+        for (int rr = 0; rr < 2; rr++) {
+            psum[rr] += __shfl_xor_sync(0xffffffffu, psum[rr], 1);
+            psum[rr] += __shfl_xor_sync(0xffffffffu, psum[rr], 2);
+            lrow[rr] += psum[rr];
+        }
+#pragma unroll
+        for (int j = 0; j < DV / 8; j++) {
+            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        }
+        // O += P V: the score fragments are the A operand as they stand
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {
+            unsigned pf[4];
+            pf[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+            pf[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+            pf[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+            pf[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+            for (int j = 0; j < DV / 8; j++) {
+                unsigned bfr[2];
+                bfr[0] = *reinterpret_cast<const unsigned *>(&Vt[j * 8 + g][kk * 16 + 2 * t]);
+                bfr[1] = *reinterpret_cast<const unsigned *>(&Vt[j * 8 + g][kk * 16 + 2 * t + 8]);
+                mma_bf16_16816(o[j], pf, bfr);
+            }
+        }
+    }
+    // normalise, gate, store
+#pragma unroll
+    for (int rr = 0; rr < 2; rr++) {
+        if (!vrow[rr]) continue;
+        const int r = r0 + warp * 16 + g + rr * 8;
+        const float inv = lrow[rr] > 0.0f ? 1.0f / lrow[rr] : 0.0f;
+        const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * DV;
+#pragma unroll
+        for (int j = 0; j < DV / 8; j++) {
+            const int d = j * 8 + 2 * t;
+            float v0 = o[j][2 * rr] * inv, v1 = o[j][2 * rr + 1] * inv;
+            if (a.gate) {
+                const float2 gv = *reinterpret_cast<const float2 *>(gate + d);
+                v0 *= 1.0f / (1.0f + expf(-gv.x));
+                v1 *= 1.0f / (1.0f + expf(-gv.y));
+            }
+            *reinterpret_cast<unsigned *>(out + (size_t)r * ldo + (size_t)h * DV + d) = pack_bf16(v0, v1);
         }
     }
 }

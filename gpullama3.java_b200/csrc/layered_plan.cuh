@@ -24,6 +24,9 @@ struct LyLayer {
     float *b_proj = nullptr;
     float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *qnorm = nullptr, *knorm = nullptr, *rel = nullptr;
     int *bucket = nullptr;
+    // TMA descriptors of the tensor-core prefill (BF16 compute mode, shapes the tcgen05 GEMM tiles cover); *_ok = usable
+    CUtensorMap m_proj, m_o, m_gate, m_up, m_down, m_att, m_h;
+    bool tc_proj = false, tc_o = false, tc_gu = false, tc_down = false;
 };
 struct LyRun {
     int layer = 0, pass = -1;
@@ -45,6 +48,15 @@ struct Layered {
     StepState *st_pf = nullptr;
     float *trace = nullptr; // [runs][cap][width], allocated on first use
     int smem_max = 0;
+    int cap_pad = 1; // rows of the activation buffers: cap, padded to whole 256-row GEMM tiles in BF16 mode
+    bool tc = false, tc_head = false;
+    bool att_mma = true; // BF16 prefill attention on the tensor cores for key/value sizes 64 and 128 (B200_LAYERED_ATT=simt: the FP32 kernel)
+    CUtensorMap m_a, m_head, m_proj_c, m_y_c, m_log_c;
+};
+
+// What ly_project needs to take the tcgen05 route: operand and result descriptors (nullptr = CUDA-core / mma.sync kernels).
+struct LyTc {
+    const CUtensorMap *a = nullptr, *b = nullptr, *b2 = nullptr, *c = nullptr;
 };
 
 static int ly_vec_f32(b200_plan *p, const b200_tensor *tensors, int nt, const std::string &name, int64_t n, float **dst, bool required = true) {
@@ -108,15 +120,29 @@ static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
     return a;
 }
 
-// C[n][N] = A[n][K] W^T with the epilogue EPI; decode (n == 1 through the graph) streams the rows, prefill takes a GEMM.
+// C[n][N] = A[n][K] W^T with the epilogue EPI; decode (n == 1 through the graph) streams the rows, prefill takes a GEMM:
+// the persistent CTA-pair tcgen05 kernel (256-wide tiles) or the single-CTA one (128-wide) of prefill_gemm.cuh when the
+// shape fits and the plan computes in BF16, else the any-shape kernels of layered.cuh.
 template <int EPI>
 static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const ly::bf16 *a16, const ly::bf16 *W, const float *bias, int N, int K,
-                      float *c32, ly::bf16 *c16, int ldc, int act) {
+                      float *c32, ly::bf16 *c16, int ldc, int act, const LyTc *tc = nullptr) {
     Layered &Y = *p->ly;
     if (decode) {
         const int warps = LY_MV_THREADS / 32;
         int grid = (N + warps - 1) / warps;
         return launch_k(p, false, ly::k_matvec_bf16<EPI>, dim3(grid), dim3(LY_MV_THREADS), (size_t)K * 4, W, bias, a32, c32, N, K, act);
+    }
+    if (tc && tc->a && !Y.f32) {
+        const int mt2 = (n + 255) / 256 * 2;
+        int rc;
+        if (EPI == ly::EPI_GATED)
+            rc = pg::gemm2_persist_launch<pg::GEMM_GATEUP, 256, pg::GEMM2_PERSIST_STAGES_256>(*tc->a, *tc->b, *tc->b2, *tc->c, c16, ldc, n, mt2, N / 128, K, p->n_sms, p->stream, 1,
+                                                                                            pg::FLAVOR_BF16 | pg::FLAVOR_GELU_BF16);
+        else if (N % 256 == 0)
+            rc = pg::gemm2_persist_launch<pg::GEMM_F32, 256, pg::GEMM2_PERSIST_STAGES_256>(*tc->a, *tc->b, *tc->b, *tc->c, c32, ldc, n, mt2, N / 256, K, p->n_sms, p->stream, 1, pg::FLAVOR_BF16);
+        else
+            rc = pg::gemm_launch<pg::GEMM_F32, pg::GEMM_STAGES>(*tc->a, *tc->b, *tc->b, *tc->c, c32, ldc, n, (n + 127) / 128, N / 128, K, p->stream, pg::FLAVOR_BF16);
+        return rc ? fail(p, B200_ERR_CUDA, "tensor-core GEMM launch failed (%d)", rc) : B200_OK;
     }
     dim3 grid((N + 63) / 64, (n + 63) / 64);
     if (Y.f32) return launch_k(p, false, ly::k_gemm_f32<EPI, float>, grid, dim3(256), (size_t)0, a32, W, bias, c32, n, N, K, ldc, act);
@@ -149,27 +175,43 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
         const LyRun &R = Y.runs[r];
         const LyLayer &L = Y.layers[R.layer];
         if ((rc = norm(r == 0, R.first && R.pass > 0, R.first ? Y.step + (size_t)R.pass * E : nullptr, L.norm1))) return rc;
-        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, L.b_proj, L.P, E, Y.PROJ, nullptr, Y.maxP, 0))) return rc;
+        LyTc t_proj, t_o, t_gu, t_down;
+        if (Y.tc && !decode) {
+            if (L.tc_proj) { t_proj.a = &Y.m_a; t_proj.b = &L.m_proj; t_proj.c = &Y.m_proj_c; }
+            if (L.tc_o) { t_o.a = &L.m_att; t_o.b = &L.m_o; t_o.c = &Y.m_y_c; }
+            if (L.tc_gu) { t_gu.a = &Y.m_a; t_gu.b = &L.m_gate; t_gu.b2 = &L.m_up; t_gu.c = &Y.m_y_c; }
+            if (L.tc_down) { t_down.a = &L.m_h; t_down.b = &L.m_down; t_down.c = &Y.m_y_c; }
+        }
+        // the q, k, v biases are added where the projection is consumed (k_qk_prep), so every projection kernel serves it
+        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, nullptr, L.P, E, Y.PROJ, nullptr, Y.maxP, 0, &t_proj))) return rc;
         nl++;
         const ly::WindowAttn wa = ly_attn_args(Y, L);
-        if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, R.kc, R.vc, st))) return rc;
+        if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, st))) return rc;
         nl++;
         const size_t asm_ = ly_att_smem(L.s, Y.ring);
-        if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
+        const bool mma64 = L.s.key_dim == 64 && L.s.value_dim == 64, mma128 = L.s.key_dim == 128 && L.s.value_dim == 128;
+        const bool aligned = Y.maxP % 4 == 0 && L.gd % 2 == 0; // float4 reads of the projection rows, paired stores
+        if (h16 && Y.att_mma && aligned && mma64 && ly::att_mma_smem_bytes<64, 64>(L.s.window) <= (size_t)Y.smem_max)
+            rc = launch_k(p, false, ly::k_window_attention_mma<64, 64>, dim3((n + 63) / 64, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<64, 64>(L.s.window),
+                          (const float *)Y.PROJ, Y.maxP, wa, (const float *)R.kc, (const float *)R.vc, st, n, Y.ATT16, L.gd);
+        else if (h16 && Y.att_mma && aligned && mma128 && ly::att_mma_smem_bytes<128, 128>(L.s.window) <= (size_t)Y.smem_max)
+            rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, dim3((n + 63) / 64, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(L.s.window),
+                          (const float *)Y.PROJ, Y.maxP, wa, (const float *)R.kc, (const float *)R.vc, st, n, Y.ATT16, L.gd);
+        else if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
                                (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd);
         else rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
                            (const float *)R.kc, (const float *)R.vc, st, Y.ATT32, L.gd);
         if (rc) return rc;
         nl++;
-        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.ATT32, Y.ATT16, L.w_o, nullptr, E, L.gd, Y.Y, nullptr, E, 0))) return rc;
+        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.ATT32, Y.ATT16, L.w_o, nullptr, E, L.gd, Y.Y, nullptr, E, 0, &t_o))) return rc;
         nl++;
         pend_y = Y.Y; pend_w = L.norm1b;
         if (L.s.ff_kind == B200_FF_DENSE_GATED) {
             if ((rc = norm(false, false, nullptr, L.norm2))) return rc;
             const int F = L.s.ff_dim;
-            if ((rc = ly_project<ly::EPI_GATED>(p, decode, n, Y.A32, Y.A16, L.w_gu, nullptr, F, E, Y.H32, h16 ? Y.H16 : nullptr, F, L.s.ff_act))) return rc;
+            if ((rc = ly_project<ly::EPI_GATED>(p, decode, n, Y.A32, Y.A16, L.w_gu, nullptr, F, E, Y.H32, h16 ? Y.H16 : nullptr, F, L.s.ff_act, &t_gu))) return rc;
             nl++;
-            if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.H32, Y.H16, L.w_down, nullptr, E, F, Y.Y, nullptr, E, 0))) return rc;
+            if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.H32, Y.H16, L.w_down, nullptr, E, F, Y.Y, nullptr, E, 0, &t_down))) return rc;
             nl++;
             pend_y = Y.Y; pend_w = L.norm2b;
         }
@@ -202,6 +244,35 @@ static int ly_capture(b200_plan *p, bool with_head, cudaGraphExec_t *exec, int *
     return B200_OK;
 }
 
+// Tensor-core prefill of BF16 plans: TMA descriptors for the weight matrices whose shapes the tcgen05 GEMM tiles cover
+// (output width a multiple of 128, reduction width a multiple of 64) and for the activation / result buffers.  A layer whose
+// shapes do not fit keeps the any-shape kernels; B200_LAYERED_TC=0 turns the route off.
+static int ly_tc_init(b200_plan *p) {
+    Layered &Y = *p->ly;
+    const char *e = getenv("B200_LAYERED_TC");
+    if ((e && e[0] == '0') || !pg::encode_fn()) return B200_OK;
+    const int E = Y.c.width, V = Y.c.vocab_size;
+    const uint64_t rows = (uint64_t)Y.cap_pad;
+    auto fits = [](int N, int K) { return N % 128 == 0 && K % 64 == 0; };
+    if (E % 64) return B200_OK;
+    bool ok = pg::make_map(&Y.m_a, Y.A16, rows, E, pg::BM) == 0 && pg::make_map_c(&Y.m_y_c, Y.Y, rows, E) == 0;
+    if (ok && Y.maxP % 4 == 0) ok = pg::make_map_c(&Y.m_proj_c, Y.PROJ, rows, Y.maxP) == 0;
+    if (!ok) return B200_OK;
+    for (LyLayer &L : Y.layers) {
+        const int F = L.s.ff_dim;
+        L.tc_proj = fits(L.P, E) && Y.maxP % 4 == 0 && pg::make_map(&L.m_proj, L.w_proj, L.P, E, 128) == 0;
+        L.tc_o = fits(E, L.gd) && pg::make_map(&L.m_o, L.w_o, E, L.gd, 128) == 0 && pg::make_map(&L.m_att, Y.ATT16, rows, L.gd, pg::BM) == 0;
+        if (L.w_gu) {
+            L.tc_gu = fits(F, E) && L.s.ff_act == B200_ACT_GELU_TANH && pg::make_map(&L.m_gate, L.w_gu, F, E, 128) == 0 &&
+                      pg::make_map(&L.m_up, L.w_gu + (size_t)F * E, F, E, 128) == 0;
+            L.tc_down = fits(E, F) && pg::make_map(&L.m_down, L.w_down, E, F, 128) == 0 && pg::make_map(&L.m_h, Y.H16, rows, F, pg::BM) == 0;
+        }
+    }
+    Y.tc_head = fits(V, E) && pg::make_map(&Y.m_head, Y.head, V, E, 128) == 0 && pg::make_map_c(&Y.m_log_c, Y.LOG, 256, V) == 0;
+    Y.tc = true;
+    return B200_OK;
+}
+
 static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_layer_spec *specs, const b200_tensor *tensors, int nt) {
     Layered *Yp = new Layered();
     p->ly = Yp;
@@ -213,6 +284,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     if (c.compute != B200_COMPUTE_BF16 && c.compute != B200_COMPUTE_F32) return fail(p, B200_ERR_BAD_ARG, "compute must be B200_COMPUTE_BF16 or B200_COMPUTE_F32");
     Y.f32 = c.compute == B200_COMPUTE_F32;
     Y.has_loop = c.loop_times >= 0;
+    { const char *e = getenv("B200_LAYERED_ATT"); Y.att_mma = !(e && e[0] == 's'); }
     if (Y.has_loop && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop)) return fail(p, B200_ERR_BAD_ARG, "loop [%d, %d) outside the %d layers", c.loop_start, c.loop_stop, c.n_layers);
     const int E = c.width;
     // the fields of b200_config the shared entry points read
@@ -264,6 +336,8 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_GATED>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention<float>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention<ly::bf16>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention_mma<64, 64>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention_mma<128, 128>, Y.smem_max));
             attrs = true;
         }
     }
@@ -360,7 +434,9 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         CK(cudaMemset(R.vc, 0, (size_t)Y.ring * L.vd * 4));
     }
     // activations
-    const size_t cap = (size_t)Y.cap, rows32 = Y.f32 ? cap : 1;
+    Y.logit_rows = Y.cap < 128 ? Y.cap : 128;
+    Y.cap_pad = Y.f32 ? Y.cap : (Y.cap + 255) / 256 * 256;
+    const size_t cap = (size_t)Y.cap_pad, rows32 = Y.f32 ? cap : 1;
     const int maxF = Y.maxF > 0 ? Y.maxF : 1;
     if ((rc = dalloc(p, &Y.X, cap * E * 4))) return rc;
     if (Y.has_loop && (rc = dalloc(p, &Y.X0, cap * E * 4))) return rc;
@@ -374,8 +450,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if ((rc = dalloc(p, &Y.ATT16, cap * Y.maxO * 2))) return rc;
         if ((rc = dalloc(p, &Y.H16, cap * maxF * 2))) return rc;
     }
-    Y.logit_rows = Y.cap < 128 ? Y.cap : 128;
-    if ((rc = dalloc(p, &Y.LOG, (size_t)Y.logit_rows * c.vocab_size * 4))) return rc;
+    if ((rc = dalloc(p, &Y.LOG, (size_t)(Y.f32 ? Y.logit_rows : 256) * c.vocab_size * 4))) return rc;
     if ((rc = dalloc(p, &Y.tok, cap * 4))) return rc;
     if ((rc = dalloc(p, &Y.rows, cap * 4))) return rc;
     if ((rc = dalloc(p, &Y.st_pf, sizeof(StepState)))) return rc;
@@ -394,6 +469,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     CK(cudaMallocHost(&p->h_st, sizeof(StepState)));
     CK(cudaMallocHost(&p->h_ids, (size_t)p->seq_cap * 4));
     p->x = Y.X;
+    if (!Y.f32 && (rc = ly_tc_init(p))) return rc;
     if ((rc = ly_capture(p, true, &p->g_decode, &p->launches_decode))) return rc;
     if ((rc = ly_capture(p, false, &p->g_prefill, nullptr))) return rc;
     CK(cudaStreamSynchronize(p->stream));
@@ -434,7 +510,9 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
         a.x = Y.X; a.w_pre = Y.final_norm; a.gather = Y.rows; a.eps = Y.c.norm_eps; a.E = E;
         a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
         if ((rc = launch_k(p, false, ly::k_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
-        if ((rc = ly_project<ly::EPI_STORE>(p, false, m, Y.A32, Y.A16, Y.head, nullptr, V, E, Y.LOG, nullptr, V, 0))) return rc;
+        LyTc t_head;
+        if (Y.tc_head) { t_head.a = &Y.m_a; t_head.b = &Y.m_head; t_head.c = &Y.m_log_c; }
+        if ((rc = ly_project<ly::EPI_STORE>(p, false, m, Y.A32, Y.A16, Y.head, nullptr, V, E, Y.LOG, nullptr, V, 0, &t_head))) return rc;
         CK(cudaMemcpyAsync(logits_out + (size_t)r0 * V, Y.LOG, (size_t)m * V * 4, cudaMemcpyDeviceToHost, p->stream));
         CK(cudaStreamSynchronize(p->stream));
     }

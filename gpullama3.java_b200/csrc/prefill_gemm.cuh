@@ -9,6 +9,7 @@
 // Warp roles (256 threads): warp 0 lane 0 = TMA producer, warp 1 lane 0 = MMA issuer, warp 2 = TMEM
 // allocator, warps 4-7 = epilogue (warp w owns TMEM lanes 32*(w%4) .. +31, i.e. 32 rows of the tile).
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -51,6 +52,21 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor for kind::f16: D = f32 (bit 4), A = B = f16 (0), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+// bits [7,10) / [10,13) select the A / B element type of kind::f16: 0 = f16, 1 = bf16
+constexpr uint32_t UMMA_IDESC_AB_BF16 = (1u << 7) | (1u << 10);
+// Run-time flavour of a launch (one kernel serves the GGUF plans and the layered plans):
+//   FLAVOR_BF16       operands are BF16 instead of FP16 (same bytes per element, same TMA maps);
+//   FLAVOR_GELU_BF16  the gate/up epilogue emits bf16(gelu_tanh(g) * u) instead of f16(silu(g) * u).
+enum { FLAVOR_BF16 = 1u, FLAVOR_GELU_BF16 = 2u };
+__device__ __forceinline__ uint32_t gated_pair(uint32_t flavor, float g0, float g1, float u0, float u1) {
+    if (flavor & FLAVOR_GELU_BF16) {
+        const float t0 = 0.7978845608028654f * fmaf(0.044715f * g0 * g0, g0, g0), t1 = 0.7978845608028654f * fmaf(0.044715f * g1 * g1, g1, g1);
+        const __nv_bfloat162 hh = __floats2bfloat162_rn(0.5f * g0 * (1.0f + tanhf(t0)) * u0, 0.5f * g1 * (1.0f + tanhf(t1)) * u1);
+        return *reinterpret_cast<const uint32_t *>(&hh);
+    }
+    const __half2 hh = __floats2half2_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+    return *reinterpret_cast<const uint32_t *>(&hh);
+}
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
 
 __device__ __forceinline__ void umma_f16(uint32_t tmem_c, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
@@ -85,7 +101,7 @@ template <int STAGES> constexpr size_t smem_bytes() { return (size_t)STAGES * (B
 template <int MODE, int STAGES>
 __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                                                          const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_c,
-                                                         void *__restrict__ Cv, int ldc, int m_valid, int K) {
+                                                         void *__restrict__ Cv, int ldc, int m_valid, int K, uint32_t flavor) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023); // SWIZZLE_128B tiles need 1024-byte alignment
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -128,7 +144,7 @@ __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant_
         }
     } else if (warp == 1 && lane == 0) {
         // ===== MMA issuer: one thread issues tcgen05.mma for the whole CTA =====
-        constexpr uint32_t idesc = umma_idesc_f16(BM, BN);
+        const uint32_t idesc = umma_idesc_f16(BM, BN) | ((flavor & FLAVOR_BF16) ? UMMA_IDESC_AB_BF16 : 0u);
         for (int kb = 0; kb < nk; kb++) {
             const int st = kb % STAGES;
             mbar_wait(full0 + 8 * st, (kb / STAGES) & 1);
@@ -163,10 +179,7 @@ __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant_
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             const float g0 = __uint_as_float(g[8 * v + 2 * e]), g1 = __uint_as_float(g[8 * v + 2 * e + 1]);
-                            const float h0 = (g0 / (1.0f + expf(-g0))) * __uint_as_float(u[8 * v + 2 * e]);
-                            const float h1 = (g1 / (1.0f + expf(-g1))) * __uint_as_float(u[8 * v + 2 * e + 1]);
-                            const __half2 hh = __floats2half2_rn(h0, h1);
-                            w[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                            w[e] = gated_pair(flavor, g0, g1, __uint_as_float(u[8 * v + 2 * e]), __uint_as_float(u[8 * v + 2 * e + 1]));
                         }
                         dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
@@ -267,7 +280,7 @@ template <int BN, int STAGES, int MT> constexpr size_t smem_bytes_2cta() {
 template <int MODE, int BN, int STAGES, int MT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
     k_gemm_f16_2cta(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_b2,
-                    const __grid_constant__ CUtensorMap tma_c, void *__restrict__ Cv, int ldc, int m_valid, int K, int kb_per_split) {
+                    const __grid_constant__ CUtensorMap tma_c, void *__restrict__ Cv, int ldc, int m_valid, int K, int kb_per_split, uint32_t flavor) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int A1_BYTES = BM * BK * 2, A_BYTES = MT * A1_BYTES, B_BYTES = (BN / 2) * BK * 2; // per CTA and stage
@@ -316,7 +329,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ===== MMA issuer: one thread of the leader CTA drives both SMs' tensor cores =====
-        constexpr uint32_t idesc = umma_idesc_f16(2 * BM, BN);
+        const uint32_t idesc = umma_idesc_f16(2 * BM, BN) | ((flavor & FLAVOR_BF16) ? UMMA_IDESC_AB_BF16 : 0u);
         for (int kb = 0; kb < nk; kb++) {
             const int st = kb % STAGES;
             mbar_wait(full0 + 8 * st, (kb / STAGES) & 1);
@@ -360,10 +373,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
                                 const float g0 = __uint_as_float(g[8 * v + 2 * e]), g1 = __uint_as_float(g[8 * v + 2 * e + 1]);
-                                const float h0 = (g0 / (1.0f + expf(-g0))) * __uint_as_float(u[8 * v + 2 * e]);
-                                const float h1 = (g1 / (1.0f + expf(-g1))) * __uint_as_float(u[8 * v + 2 * e + 1]);
-                                const __half2 hh = __floats2half2_rn(h0, h1);
-                                w[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                                w[e] = gated_pair(flavor, g0, g1, __uint_as_float(u[8 * v + 2 * e]), __uint_as_float(u[8 * v + 2 * e + 1]));
                             }
                             dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
@@ -432,7 +442,7 @@ template <int BN, int STAGES> constexpr size_t smem_bytes_2cta_persist() {
 template <int MODE, int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
     k_gemm_f16_2cta_persist(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_b2,
-                            const __grid_constant__ CUtensorMap tma_c, void *__restrict__ Cv, int ldc, int m_valid, int K, int m_pairs, int n_tiles, int splits) {
+                            const __grid_constant__ CUtensorMap tma_c, void *__restrict__ Cv, int ldc, int m_valid, int K, int m_pairs, int n_tiles, int splits, uint32_t flavor) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2, CST_BYTES = BM * 32 * 4;
@@ -483,7 +493,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ===== MMA issuer (leader): accumulator buffer i & 1 =====
-        constexpr uint32_t idesc = umma_idesc_f16(2 * BM, BN);
+        const uint32_t idesc = umma_idesc_f16(2 * BM, BN) | ((flavor & FLAVOR_BF16) ? UMMA_IDESC_AB_BF16 : 0u);
         int it = 0, i = 0;
         for (int t = cid; t < total; t += n_clusters, i++) {
             const int buf = i & 1;
@@ -536,10 +546,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
                                 const float g0 = __uint_as_float(g[8 * v + 2 * e]), g1 = __uint_as_float(g[8 * v + 2 * e + 1]);
-                                const float h0 = (g0 / (1.0f + expf(-g0))) * __uint_as_float(u[8 * v + 2 * e]);
-                                const float h1 = (g1 / (1.0f + expf(-g1))) * __uint_as_float(u[8 * v + 2 * e + 1]);
-                                const __half2 hh = __floats2half2_rn(h0, h1);
-                                w[e] = *reinterpret_cast<const uint32_t *>(&hh);
+                                w[e] = gated_pair(flavor, g0, g1, __uint_as_float(u[8 * v + 2 * e]), __uint_as_float(u[8 * v + 2 * e + 1]));
                             }
                             dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
@@ -634,20 +641,20 @@ inline int make_map_c(CUtensorMap *map, const void *base, uint64_t rows, uint64_
 
 template <int MODE, int STAGES>
 inline int gemm_launch(const CUtensorMap &a, const CUtensorMap &b, const CUtensorMap &b2, const CUtensorMap &c, void *C, int ldc, int m_valid, int m_tiles,
-                       int n_tiles, int K, cudaStream_t stream) {
+                       int n_tiles, int K, cudaStream_t stream, uint32_t flavor = 0) {
     static bool attr = false; // one flag per instantiation
     if (!attr) {
         if (cudaFuncSetAttribute(k_gemm_f16_tcgen05<MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<STAGES>()) != cudaSuccess) return -4;
         attr = true;
     }
-    k_gemm_f16_tcgen05<MODE, STAGES><<<dim3(m_tiles, n_tiles), 256, smem_bytes<STAGES>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K);
+    k_gemm_f16_tcgen05<MODE, STAGES><<<dim3(m_tiles, n_tiles), 256, smem_bytes<STAGES>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, flavor);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 // m_tiles = 128-row tiles of M, a multiple of 2 * MT (M padded to MT * 256).  B maps must have box rows = BN / 2.
 template <int MODE, int BN, int STAGES, int MT = 1>
 inline int gemm2_launch(const CUtensorMap &a, const CUtensorMap &b, const CUtensorMap &b2, const CUtensorMap &c, void *C, int ldc, int m_valid, int m_tiles,
-                        int n_tiles, int K, cudaStream_t stream, int splits = 1) {
+                        int n_tiles, int K, cudaStream_t stream, int splits = 1, uint32_t flavor = 0) {
     static bool attr = false;
     if (!attr) {
         if (cudaFuncSetAttribute(k_gemm_f16_2cta<MODE, BN, STAGES, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_2cta<BN, STAGES, MT>()) != cudaSuccess)
@@ -657,7 +664,7 @@ inline int gemm2_launch(const CUtensorMap &a, const CUtensorMap &b, const CUtens
     if (m_tiles % (2 * MT) || splits < 1 || (splits > 1 && MODE != GEMM_RESID)) return -6;
     const int nk = (K + BK - 1) / BK, per = (nk + splits - 1) / splits;
     if ((splits - 1) * per >= nk) return -6; // an empty split would publish an unwritten accumulator
-    k_gemm_f16_2cta<MODE, BN, STAGES, MT><<<dim3(m_tiles / MT, n_tiles, splits), 256, smem_bytes_2cta<BN, STAGES, MT>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, per);
+    k_gemm_f16_2cta<MODE, BN, STAGES, MT><<<dim3(m_tiles / MT, n_tiles, splits), 256, smem_bytes_2cta<BN, STAGES, MT>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, per, flavor);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 constexpr int GEMM2_STAGES_256 = 6, GEMM2_STAGES_128 = 8; // 192 KB of operand ring per CTA either way
@@ -666,7 +673,7 @@ constexpr int GEMM2_STAGES_256_M2 = 4;                    // 4 x (32 KB of A + 1
 // Persistent variant (round-2 candidate).  n_sms: SMs of the device; the grid is the largest even number of CTAs <= n_sms.
 template <int MODE, int BN, int STAGES>
 inline int gemm2_persist_launch(const CUtensorMap &a, const CUtensorMap &b, const CUtensorMap &b2, const CUtensorMap &c, void *C, int ldc, int m_valid, int m_tiles,
-                                int n_tiles, int K, int n_sms, cudaStream_t stream, int splits = 1) {
+                                int n_tiles, int K, int n_sms, cudaStream_t stream, int splits = 1, uint32_t flavor = 0) {
     static bool attr = false;
     if (!attr) {
         if (cudaFuncSetAttribute(k_gemm_f16_2cta_persist<MODE, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes_2cta_persist<BN, STAGES>()) !=
@@ -683,7 +690,7 @@ inline int gemm2_persist_launch(const CUtensorMap &a, const CUtensorMap &b, cons
     int clusters = n_sms / 2;
     if (clusters > total) clusters = total;
     if (clusters < 1) return -6;
-    k_gemm_f16_2cta_persist<MODE, BN, STAGES><<<dim3(2 * clusters), 256, smem_bytes_2cta_persist<BN, STAGES>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, m_pairs, n_tiles, splits);
+    k_gemm_f16_2cta_persist<MODE, BN, STAGES><<<dim3(2 * clusters), 256, smem_bytes_2cta_persist<BN, STAGES>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, m_pairs, n_tiles, splits, flavor);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 constexpr int GEMM2_PERSIST_STAGES_256 = 5; // 5 x 32 KB of operands + 2 x 16 KB of C staging

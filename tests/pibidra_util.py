@@ -47,6 +47,9 @@ def configs(S):
         "loop_once_end": (S.pibidra_config(40, 64, [L(2, 2, 20, 20, 11, 64), L(5, 1, 8, 8, 2, None)], loop=(1, 2, 1), embedding_scale=1.0), 4),
         "window_one": (S.pibidra_config(32, 40, [L(2, 1, 16, 16, 1, 48), L(2, 1, 16, 16, 64, 48)]), 16),
         "big_head": (S.pibidra_config(72, 70, [L(1, 1, 40, 160, 10, 100, bias_max=9.0)]), 12),
+        # shapes the tensor-core prefill kernels take (head sizes 64 / 128, widths in whole GEMM tiles), windows that end inside a key tile
+        "tiles64": (S.pibidra_config(128, 256, [L(2, 1, 64, 64, 70, 256, bias_max=100.0), L(2, 1, 64, 64, 9, 256)], loop=(0, 2, 2)), 14),
+        "tiles128": (S.pibidra_config(256, 384, [L(2, 2, 128, 128, 33, 128, bias_max=40.0), L(2, 1, 128, 128, 129, 384, bias_max=200.0)]), 8),
     }
 
 

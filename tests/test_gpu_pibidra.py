@@ -37,7 +37,7 @@ def assert_rows(got, ref, tol, what=""):
 
 
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["plain", "loop_mid", "loop_start_odd", "loop_once_end", "window_one", "big_head"])
+@pytest.mark.parametrize("name", ["plain", "loop_mid", "loop_start_odd", "loop_once_end", "window_one", "big_head", "tiles64", "tiles128"])
 def test_every_layer_run_matches_oracle(pkg, name, compute):
     """Residual stream after every layer run and the logits: each mechanism, in the order the runs apply them."""
     S, O = pkg.synth, oracle()
@@ -97,6 +97,31 @@ def test_portions_of_every_size(pkg, compute):
                 got.append(plan.forward_decode(toks[p], p)[0][None])
                 p += 1
             assert_rows(np.concatenate(got), ref, TOL[compute], f"portions {sizes}")
+    finally:
+        plan.free()
+
+
+@pytest.mark.parametrize("name", ["tiles64", "tiles128"])
+@pytest.mark.parametrize("compute", ["float32", "bfloat16"])
+def test_tensor_core_prefill_shapes(pkg, name, compute):
+    """Head sizes and widths that take the tcgen05 GEMMs and the tensor-core attention in BF16 mode: a prompt longer than
+    several key tiles, whole and in ragged portions (one of them a single row of a 64-row tile), then decoded."""
+    S, O = pkg.synth, oracle()
+    cfg, rows = configs(S)[name]
+    w = S.pibidra_weights(cfg, 21, bias_rows=rows)
+    toks = np.random.default_rng(12).integers(0, cfg["vocab"], 230).tolist()
+    ref = O.forward(cfg, w64(w), toks)
+    plan = make_plan(pkg, cfg, w, ctx=256, batch=100, compute=compute)
+    try:
+        assert_rows(prefill_all(plan, toks, 100), ref, TOL[compute], "whole")
+        got, p = [], 0
+        for m in (65, 2, 100, 1, 37):
+            got.append(prefill_all(plan, toks[p:p + m], 100, start=p))
+            p += m
+        while p < len(toks):
+            got.append(plan.forward_decode(toks[p], p)[0][None])
+            p += 1
+        assert_rows(np.concatenate(got), ref, TOL[compute], "portions")
     finally:
         plan.free()
 
