@@ -358,7 +358,7 @@ struct WindowAttn {
 // One CTA per row: projection biases, RMS statistics over the WHOLE q and the WHOLE k projection, q normalised in place,
 // k / v into the ring.
 __global__ void __launch_bounds__(256) k_qk_prep(float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ bias, float *__restrict__ kc,
-                                                 float *__restrict__ vc, const StepState *__restrict__ st) {
+                                                 float *__restrict__ vc, bf16 *__restrict__ kc16, bf16 *__restrict__ vc16, const StepState *__restrict__ st) {
     __shared__ float red[32];
     const int r = blockIdx.x, tid = threadIdx.x;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
@@ -382,50 +382,92 @@ __global__ void __launch_bounds__(256) k_qk_prep(float *__restrict__ P, int ldp,
         kinv = 1.0f / sqrtf(ss / (float)kd + a.eps);
     }
     for (int i = tid; i < qd; i += 256) q[i] = a.qnorm ? q[i] * qinv * a.qnorm[i] : q[i];
-    for (int i = tid; i < kd; i += 256) kc[(size_t)slot * kd + i] = a.knorm ? k[i] * kinv * a.knorm[i] : k[i];
-    for (int i = tid; i < vd; i += 256) vc[(size_t)slot * vd + i] = v[i];
+    for (int i = tid; i < kd; i += 256) {
+        const float kv = a.knorm ? k[i] * kinv * a.knorm[i] : k[i];
+        kc[(size_t)slot * kd + i] = kv;
+        if (kc16) kc16[(size_t)slot * kd + i] = __float2bfloat16_rn(kv); // BF16 twin row for the tensor-core prefill attention
+    }
+    for (int i = tid; i < vd; i += 256) {
+        vc[(size_t)slot * vd + i] = v[i];
+        if (vc16) vc16[(size_t)slot * vd + i] = __float2bfloat16_rn(v[i]);
+    }
 }
 
 // One CTA per (row, head): scores of the window into shared memory, softmax with the sink term, weighted value sum, gate.
-// Dynamic shared memory: dk + min(window, ring) + LY_ATT_THREADS floats.
-#define LY_ATT_THREADS 128
+// Scores: a group of dk/4 lanes (at most a warp) owns a key and reads its row with coalesced 128-bit loads; values: a group of
+// dv/4 threads owns every groups-th key.  Sizes that are no multiple of 4 take scalar loads.
+// Dynamic shared memory: att_smem_floats(dk, window) floats.
+#define LY_ATT_THREADS 256
+__host__ __device__ inline size_t att_smem_floats(int dk, int window) { return (size_t)((dk + 3) / 4 * 4) + window + 4 * LY_ATT_THREADS; }
+
 template <typename OUT_T>
 __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ kc,
                                                                      const float *__restrict__ vc, const StepState *__restrict__ st,
                                                                      OUT_T *__restrict__ out, int ldo) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[32];
-    const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
     const int g = h / (a.heads / a.kv_heads);
     const int pos = st->pos + r;
     const int lo = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
     const int nk = pos - lo + 1;
-    float *qs = sm, *sc = sm + a.dk, *part = sc + a.window;
+    float *qs = sm, *sc = sm + (a.dk + 3) / 4 * 4, *part = sc + a.window;
     const float *q = P + (size_t)r * ldp + (size_t)h * a.dk;
     for (int i = tid; i < a.dk; i += LY_ATT_THREADS) qs[i] = q[i];
     __syncthreads();
-    // scores: one key per thread
-    float mx = 0.0f; // the sink's logit; without a sink the maximum is taken over the keys alone
-    if (!a.sink) mx = -INFINITY;
-    const bool vec = (a.dk & 3) == 0 && (kd & 3) == 0;
-    for (int j = tid; j < nk; j += LY_ATT_THREADS) {
-        const int p = lo + j;
-        const float *kr = kc + (size_t)(p % a.ring) * kd + (size_t)g * a.dk;
-        float d = 0.0f;
-        if (vec) {
-            for (int i = 0; i < a.dk; i += 4) {
-                const float4 kv = *reinterpret_cast<const float4 *>(kr + i);
-                d = fmaf(qs[i], kv.x, d); d = fmaf(qs[i + 1], kv.y, d); d = fmaf(qs[i + 2], kv.z, d); d = fmaf(qs[i + 3], kv.w, d);
+    float mx = a.sink ? 0.0f : -INFINITY; // the sink's logit takes part in the maximum
+    {
+        const bool vec = (a.dk & 3) == 0 && (kd & 3) == 0;
+        int lpk = 32; // lanes per key
+        if (vec) { lpk = 1; while (lpk < a.dk / 4 && lpk < 32) lpk <<= 1; }
+        const int kpw = 32 / lpk, sub = lane % lpk, ks = lane / lpk;
+        const int stride = (LY_ATT_THREADS / 32) * kpw; // keys per CTA-wide step
+        auto finish = [&](int j, float d) { // after the lane reduction: cap, bias, store (one lane per key)
+            float e = d * a.scale;
+            if (a.softcap > 0.0f) e = a.softcap * tanhf(e / a.softcap);
+            if (a.rel) e += a.rel[(size_t)a.bucket[pos - lo - j] * a.heads + h];
+            sc[j] = e;
+            mx = fmaxf(mx, e);
+        };
+        if (vec && a.dk <= 128) { // one 128-bit chunk per lane and key: four keys in flight per lane
+            const bool has = sub < a.dk / 4;
+            const float4 qv = has ? *reinterpret_cast<const float4 *>(qs + 4 * sub) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j0 = warp * kpw; j0 < nk; j0 += 4 * stride) {
+                float4 kv[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = j0 + u * stride + ks;
+                    kv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (has && j < nk) kv[u] = *reinterpret_cast<const float4 *>(kc + (size_t)((lo + j) % a.ring) * kd + (size_t)g * a.dk + 4 * sub);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = j0 + u * stride + ks;
+                    float d = fmaf(qv.x, kv[u].x, fmaf(qv.y, kv[u].y, fmaf(qv.z, kv[u].z, qv.w * kv[u].w)));
+                    for (int o = lpk >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                    if (j < nk && sub == 0) finish(j, d);
+                }
             }
         } else {
-            for (int i = 0; i < a.dk; i++) d = fmaf(qs[i], kr[i], d);
+            for (int j0 = warp * kpw; j0 < nk; j0 += stride) {
+                const int j = j0 + ks;
+                float d = 0.0f;
+                if (j < nk) {
+                    const float *kr = kc + (size_t)((lo + j) % a.ring) * kd + (size_t)g * a.dk;
+                    if (vec) {
+                        for (int c = sub; c < a.dk / 4; c += lpk) {
+                            const float4 kv = *reinterpret_cast<const float4 *>(kr + 4 * c), qv = *reinterpret_cast<const float4 *>(qs + 4 * c);
+                            d = fmaf(qv.x, kv.x, d); d = fmaf(qv.y, kv.y, d); d = fmaf(qv.z, kv.z, d); d = fmaf(qv.w, kv.w, d);
+                        }
+                    } else {
+                        for (int i = sub; i < a.dk; i += lpk) d = fmaf(qs[i], kr[i], d);
+                    }
+                }
+                for (int o = lpk >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                if (j < nk && sub == 0) finish(j, d);
+            }
         }
-        float e = d * a.scale;
-        if (a.softcap > 0.0f) e = a.softcap * tanhf(e / a.softcap);
-        if (a.rel) e += a.rel[(size_t)a.bucket[pos - p] * a.heads + h];
-        sc[j] = e;
-        mx = fmaxf(mx, e);
     }
     mx = block_max(mx, red);
     float sum = 0.0f;
@@ -436,66 +478,116 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     }
     sum = block_sum(sum, red); // also orders the sc[] writes before the reads below
     const float inv = 1.0f / (sum + (a.sink ? expf(-mx) : 0.0f));
-    // weighted values: thread groups of dv lanes take every groups-th key
-    const int groups = a.dv >= LY_ATT_THREADS ? 1 : LY_ATT_THREADS / a.dv;
     const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * a.dv;
-    for (int d0 = 0; d0 < a.dv; d0 += LY_ATT_THREADS) {
-        const int grp = a.dv >= LY_ATT_THREADS ? 0 : tid / a.dv;
-        const int d = a.dv >= LY_ATT_THREADS ? d0 + tid : tid % a.dv;
-        float acc = 0.0f;
-        if (d < a.dv && grp < groups)
-            for (int j = grp; j < nk; j += groups) acc = fmaf(sc[j], vc[(size_t)((lo + j) % a.ring) * vd + (size_t)g * a.dv + d], acc);
-        if (groups > 1) {
-            part[tid] = acc;
-            __syncthreads();
-            if (tid < a.dv) {
-                for (int k = 1; k < groups; k++) acc += part[tid + k * a.dv];
+    const int vw = ((a.dv & 3) == 0 && (vd & 3) == 0) ? 4 : 1; // value elements per thread
+    int tpk = (a.dv + vw - 1) / vw;                             // threads per key
+    if (tpk > LY_ATT_THREADS) tpk = LY_ATT_THREADS;
+    const int groups = LY_ATT_THREADS / tpk, grp = tid / tpk, dl = tid % tpk;
+    for (int db = 0; db < a.dv; db += tpk * vw) {
+        const int d = db + dl * vw;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (grp < groups && d < a.dv) {
+#pragma unroll 4
+            for (int j = grp; j < nk; j += groups) {
+                const float *vr = vc + (size_t)((lo + j) % a.ring) * vd + (size_t)g * a.dv + d;
+                const float w = sc[j];
+                if (vw == 4) {
+                    const float4 v = *reinterpret_cast<const float4 *>(vr);
+                    acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]); acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+                } else acc[0] = fmaf(w, vr[0], acc[0]);
             }
-            __syncthreads();
         }
+        __syncthreads(); // part is reused per value block
+#pragma unroll
+        for (int e = 0; e < 4; e++) part[e * LY_ATT_THREADS + tid] = acc[e];
+        __syncthreads();
         if (grp == 0 && d < a.dv) {
-            float o = acc * inv;
-            if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d]));
-            store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d, o);
+            for (int e = 0; e < vw; e++) {
+                float o = 0.0f;
+                for (int k = 0; k < groups; k++) o += part[e * LY_ATT_THREADS + k * tpk + dl];
+                o *= inv;
+                if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d + e]));
+                store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d + e, o);
+            }
         }
     }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// The same attention for a prefill chunk on the tensor cores (BF16 compute mode): one CTA per (64 query rows, head), four
-// warps of 16 rows; key tiles of 64 positions are read from the FP32 ring, rounded to BF16 in shared memory (K as [key][d],
-// V transposed to [d][key]) and multiplied with mma.sync m16n8k16; scores, cap, distance bias, mask and the ONLINE softmax
-// stay in FP32 registers.  The sink is the initial state of the running softmax: maximum 0, denominator exp(0) = 1, no value.
-// Dynamic shared memory: att_mma_smem_bytes<DK, DV>(window).
+// The same attention for a prefill chunk on the tensor cores (BF16 compute mode): one CTA per (128 query rows, head), eight
+// warps of 16 rows (two warps per scheduler: a lone warp cannot hide the latency of its own dependent instructions).  Keys and values come from the BF16 twin rows of the ring (written by k_qk_prep next to the FP32 rows the
+// decode step reads): key tiles of 64 positions travel global -> shared with cp.async, double buffered, so the copy of tile
+// i + 1 overlaps the mma.sync m16n8k16 work on tile i; V fragments are read with ldmatrix.trans.  Scores, cap, distance bias,
+// mask and the ONLINE softmax stay in FP32 registers.  The sink is the initial state of the running softmax: maximum 0,
+// denominator exp(0) = 1, no value.  Dynamic shared memory: att_mma_smem_bytes<DK, DV>(window).
 // ---------------------------------------------------------------------------------------------------------------------
-#define LY_ATT_MMA_THREADS 128
+#define LY_ATT_MMA_ROWS 128 // query rows per CTA: eight warps of 16 rows share every key tile
+#define LY_ATT_MMA_THREADS (LY_ATT_MMA_ROWS * 2)
 template <int DK, int DV> __host__ __device__ constexpr size_t att_mma_smem_bytes(int window) {
-    return (size_t)(64 * (DK + 8) * 2) * 2 + (size_t)DV * (64 + 8) * 2 + (size_t)window * 4;
+    return (size_t)(LY_ATT_MMA_ROWS * (DK + 8) * 2) + (size_t)(64 * (DK + 8) * 2) * 2 + (size_t)(64 * (DV + 8) * 2) * 2 + (size_t)window * 4;
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned *>(&v);
 }
+// tanh(x) = 1 - 2 / (1 + exp(2x)) with the hardware exponential: absolute error ~1e-7, far below the BF16 rounding of the
+// operands that produced x (the FP32 kernels keep tanhf)
+__device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, bool valid) { // 16 bytes, zero-filled when !valid
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(unsigned (&r)[2], const void *row) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(const float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ kc,
-                                                                             const float *__restrict__ vc, const StepState *__restrict__ st, int n,
+__global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(const float *__restrict__ P, int ldp, WindowAttn a, const bf16 *__restrict__ kc16,
+                                                                             const bf16 *__restrict__ vc16, const StepState *__restrict__ st, int n,
                                                                              bf16 *__restrict__ out, int ldo) {
     extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int BM = LY_ATT_MMA_ROWS;
+    constexpr int QT = BM * (DK + 8) * 2, KT = 64 * (DK + 8) * 2, VT = 64 * (DV + 8) * 2; // bytes of the Q tile, one K tile, one V tile
     bf16(*Qs)[DK + 8] = reinterpret_cast<bf16(*)[DK + 8]>(smraw);
-    bf16(*Ks)[DK + 8] = reinterpret_cast<bf16(*)[DK + 8]>(smraw + 64 * (DK + 8) * 2);
-    bf16(*Vt)[64 + 8] = reinterpret_cast<bf16(*)[64 + 8]>(smraw + 2 * 64 * (DK + 8) * 2);
-    float *sbias = reinterpret_cast<float *>(smraw + 2 * 64 * (DK + 8) * 2 + DV * (64 + 8) * 2);
+    float *sbias = reinterpret_cast<float *>(smraw + QT + 2 * KT + 2 * VT);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int h = blockIdx.y, r0 = blockIdx.x * 64;
+    const int h = blockIdx.y, r0 = blockIdx.x * BM;
     const int kd = a.kv_heads * DK, vd = a.kv_heads * DV, qd = a.heads * DK;
     const int kvh = h / (a.heads / a.kv_heads);
     const int pos0 = st->pos;
-    const int rows = n - r0 < 64 ? n - r0 : 64;
-    // distance -> bias of this head
-    for (int d = tid; d < a.window; d += LY_ATT_MMA_THREADS) sbias[d] = a.rel ? a.rel[(size_t)a.bucket[d] * a.heads + h] : 0.0f;
+    const int rows = n - r0 < BM ? n - r0 : BM;
+    const int q_lo = pos0 + r0, q_hi = pos0 + r0 + rows - 1;
+    const int k_lo = q_lo - a.window + 1 > 0 ? q_lo - a.window + 1 : 0;
+    auto load_tile = [&](int buf, int kt0) {
+        bf16(*Kd)[DK + 8] = reinterpret_cast<bf16(*)[DK + 8]>(smraw + QT + buf * KT);
+        bf16(*Vd)[DV + 8] = reinterpret_cast<bf16(*)[DV + 8]>(smraw + QT + 2 * KT + buf * VT);
+        const int slot0 = kt0 % a.ring; // one division per tile; rows wrap by subtraction (by division only in rings below 64 slots)
+        for (int e = tid; e < 64 * (DK / 8); e += LY_ATT_MMA_THREADS) {
+            const int r = e / (DK / 8), c = (e % (DK / 8)) * 8;
+            const bool ok = kt0 + r <= q_hi;
+            int sl = slot0 + r;
+            if (sl >= a.ring) sl = a.ring >= 64 ? sl - a.ring : sl % a.ring;
+            cp_async16(&Kd[r][c], kc16 + (ok ? (size_t)sl * kd + (size_t)kvh * DK + c : 0), ok);
+        }
+        for (int e = tid; e < 64 * (DV / 8); e += LY_ATT_MMA_THREADS) {
+            const int r = e / (DV / 8), c = (e % (DV / 8)) * 8;
+            const bool ok = kt0 + r <= q_hi;
+            int sl = slot0 + r;
+            if (sl >= a.ring) sl = a.ring >= 64 ? sl - a.ring : sl % a.ring;
+            cp_async16(&Vd[r][c], vc16 + (ok ? (size_t)sl * vd + (size_t)kvh * DV + c : 0), ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(0, k_lo);
+    // distance -> bias of this head, for the distances this tile of rows can see
+    {
+        const int dmax = q_hi - k_lo + 1 < a.window ? q_hi - k_lo + 1 : a.window;
+        for (int d = tid; d < dmax; d += LY_ATT_MMA_THREADS) sbias[d] = a.rel ? a.rel[(size_t)a.bucket[d] * a.heads + h] : 0.0f;
+    }
     // Q tile -> BF16
-    for (int e = tid; e < 64 * (DK / 4); e += LY_ATT_MMA_THREADS) {
+    for (int e = tid; e < BM * (DK / 4); e += LY_ATT_MMA_THREADS) {
         const int r = e / (DK / 4), c = (e % (DK / 4)) * 4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < rows) v = *reinterpret_cast<const float4 *>(P + (size_t)(r0 + r) * ldp + (size_t)h * DK + c);
@@ -523,99 +615,94 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
     lrow[0] = lrow[1] = a.sink ? 1.0f : 0.0f;
     const int prow[2] = {pos0 + r0 + warp * 16 + g, pos0 + r0 + warp * 16 + g + 8}; // positions of this thread's two rows
     const bool vrow[2] = {warp * 16 + g < rows, warp * 16 + g + 8 < rows};
-    const int q_lo = pos0 + r0, q_hi = pos0 + r0 + rows - 1;
-    const int k_lo = q_lo - a.window + 1 > 0 ? q_lo - a.window + 1 : 0;
+    const int w_lo = pos0 + r0 + warp * 16, w_hi = w_lo + 15; // positions of this warp's rows
     const float inv_cap = a.softcap > 0.0f ? 1.0f / a.softcap : 0.0f;
-    for (int kt0 = k_lo; kt0 <= q_hi; kt0 += 64) {
-        __syncthreads(); // the previous tile's fragments have been read
-        for (int e = tid; e < 64 * (DK / 4); e += LY_ATT_MMA_THREADS) {
-            const int r = e / (DK / 4), c = (e % (DK / 4)) * 4, p = kt0 + r;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (p <= q_hi) v = *reinterpret_cast<const float4 *>(kc + (size_t)(p % a.ring) * kd + (size_t)kvh * DK + c);
-            *reinterpret_cast<uint2 *>(&Ks[r][c]) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
-        }
-        for (int e = tid; e < 64 * (DV / 4); e += LY_ATT_MMA_THREADS) {
-            const int r = e / (DV / 4), c = (e % (DV / 4)) * 4, p = kt0 + r;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (p <= q_hi) v = *reinterpret_cast<const float4 *>(vc + (size_t)(p % a.ring) * vd + (size_t)kvh * DV + c);
-            Vt[c][r] = __float2bfloat16_rn(v.x); Vt[c + 1][r] = __float2bfloat16_rn(v.y);
-            Vt[c + 2][r] = __float2bfloat16_rn(v.z); Vt[c + 3][r] = __float2bfloat16_rn(v.w);
-        }
+    int buf = 0;
+    for (int kt0 = k_lo; kt0 <= q_hi; kt0 += 64, buf ^= 1) {
+        if (kt0 + 64 <= q_hi) {
+            load_tile(buf ^ 1, kt0 + 64); // the other buffer was released by the barrier that ended the previous iteration
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        // S = Q K^T for this warp's 16 rows x 64 keys
-        float sc[8][4];
+        // a warp whose rows see no key of this tile (all later, or all beyond the window) skips the arithmetic
+        if (kt0 <= w_hi && kt0 + 63 > w_lo - a.window) {
+            bf16(*Ks)[DK + 8] = reinterpret_cast<bf16(*)[DK + 8]>(smraw + QT + buf * KT);
+            bf16(*Vs)[DV + 8] = reinterpret_cast<bf16(*)[DV + 8]>(smraw + QT + 2 * KT + buf * VT);
+            // S = Q K^T for this warp's 16 rows x 64 keys
+            float sc[8][4];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
+            for (int j = 0; j < 8; j++) {
 #pragma unroll
-            for (int e = 0; e < 4; e++) sc[j][e] = 0.0f;
+                for (int e = 0; e < 4; e++) sc[j][e] = 0.0f;
 #pragma unroll
-            for (int kk = 0; kk < DK / 16; kk++) {
-                unsigned bfr[2];
-                bfr[0] = *reinterpret_cast<const unsigned *>(&Ks[j * 8 + g][kk * 16 + 2 * t]);
-                bfr[1] = *reinterpret_cast<const unsigned *>(&Ks[j * 8 + g][kk * 16 + 2 * t + 8]);
-                mma_bf16_16816(sc[j], qf[kk], bfr);
+                for (int kk = 0; kk < DK / 16; kk++) {
+                    unsigned bfr[2];
+                    bfr[0] = *reinterpret_cast<const unsigned *>(&Ks[j * 8 + g][kk * 16 + 2 * t]);
+                    bfr[1] = *reinterpret_cast<const unsigned *>(&Ks[j * 8 + g][kk * 16 + 2 * t + 8]);
+                    mma_bf16_16816(sc[j], qf[kk], bfr);
+                }
             }
-        }
-        // cap, bias, mask; tile maximum per row
-        float tmax[2] = {-INFINITY, -INFINITY};
+            // cap, bias, mask; tile maximum per row
+            float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < 8; j++)
+            for (int j = 0; j < 8; j++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int rr = e >> 1, pj = kt0 + j * 8 + 2 * t + (e & 1), dist = prow[rr] - pj;
-                float v = sc[j][e] * a.scale;
-                if (a.softcap > 0.0f) v = a.softcap * tanhf(v * inv_cap);
-                if (vrow[rr] && dist >= 0 && dist < a.window) v += sbias[dist];
-                else v = -INFINITY;
-                sc[j][e] = v;
-                tmax[rr] = fmaxf(tmax[rr], v);
+                for (int e = 0; e < 4; e++) {
+                    const int rr = e >> 1, pj = kt0 + j * 8 + 2 * t + (e & 1), dist = prow[rr] - pj;
+                    float v = sc[j][e] * a.scale;
+                    if (a.softcap > 0.0f) v = a.softcap * tanh_fast(v * inv_cap);
+                    if (vrow[rr] && dist >= 0 && dist < a.window) v += sbias[dist];
+                    else v = -INFINITY;
+                    sc[j][e] = v;
+                    tmax[rr] = fmaxf(tmax[rr], v);
+                }
+            float corr[2], muse[2];
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
+                tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
+                const float mnew = fmaxf(mrow[rr], tmax[rr]);
+                muse[rr] = mnew == -INFINITY ? 0.0f : mnew;
+                corr[rr] = mrow[rr] == -INFINITY ? 0.0f : __expf(mrow[rr] - muse[rr]);
+                mrow[rr] = mnew;
+                lrow[rr] *= corr[rr];
             }
-        float corr[2], muse[2];
+            float psum[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int rr = 0; rr < 2; rr++) {
-            tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
-            tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
-            const float mnew = fmaxf(mrow[rr], tmax[rr]);
-            muse[rr] = mnew == -INFINITY ? 0.0f : mnew;
-            corr[rr] = mrow[rr] == -INFINITY ? 0.0f : expf(mrow[rr] - muse[rr]);
-            mrow[rr] = mnew;
-            lrow[rr] *= corr[rr];
-        }
-        float psum[2] = {0.0f, 0.0f};
+            for (int j = 0; j < 8; j++)
 #pragma unroll
-        for (int j = 0; j < 8; j++)
+                for (int e = 0; e < 4; e++) {
+                    const float pv = __expf(sc[j][e] - muse[e >> 1]); // exp(-inf) = 0 for masked entries
+                    sc[j][e] = pv;
+                    psum[e >> 1] += pv;
+                }
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float pv = expf(sc[j][e] - muse[e >> 1]); // exp(-inf) = 0 for masked entries
-                sc[j][e] = pv;
-                psum[e >> 1] += pv;
+            for (int rr = 0; rr < 2; rr++) {
+                psum[rr] += __shfl_xor_sync(0xffffffffu, psum[rr], 1);
+                psum[rr] += __shfl_xor_sync(0xffffffffu, psum[rr], 2);
+                lrow[rr] += psum[rr];
             }
-#pragma unroll
-        for (int rr = 0; rr < 2; rr++) {
-            psum[rr] += __shfl_xor_sync(0xffffffffu, psum[rr], 1);
-            psum[rr] += __shfl_xor_sync(0xffffffffu, psum[rr], 2);
-            lrow[rr] += psum[rr];
-        }
-#pragma unroll
-        for (int j = 0; j < DV / 8; j++) {
-            o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
-        }
-        // O += P V: the score fragments are the A operand as they stand
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++) {
-            unsigned pf[4];
-            pf[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
-            pf[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
-            pf[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
-            pf[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
 #pragma unroll
             for (int j = 0; j < DV / 8; j++) {
-                unsigned bfr[2];
-                bfr[0] = *reinterpret_cast<const unsigned *>(&Vt[j * 8 + g][kk * 16 + 2 * t]);
-                bfr[1] = *reinterpret_cast<const unsigned *>(&Vt[j * 8 + g][kk * 16 + 2 * t + 8]);
-                mma_bf16_16816(o[j], pf, bfr);
+                o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
+            }
+            // O += P V: the score fragments are the A operand as they stand; V[key][d] becomes the B operand through ldmatrix.trans
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                unsigned pf[4];
+                pf[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+                pf[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+                pf[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                pf[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+                for (int j = 0; j < DV / 8; j++) {
+                    unsigned bfr[2];
+                    ldmatrix_x2_trans(bfr, &Vs[kk * 16 + (lane & 15)][j * 8]);
+                    mma_bf16_16816(o[j], pf, bfr);
+                }
             }
         }
+        __syncthreads(); // every warp is done with this buffer before the next iteration's copy lands in it
     }
     // normalise, gate, store
 #pragma unroll

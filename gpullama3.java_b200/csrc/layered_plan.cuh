@@ -32,6 +32,7 @@ struct LyRun {
     int layer = 0, pass = -1;
     bool first = false; // first layer of a loop pass
     float *kc = nullptr, *vc = nullptr;
+    ly::bf16 *kc16 = nullptr, *vc16 = nullptr; // BF16 twin rows (BF16 plans whose head sizes the tensor-core attention takes)
 };
 struct Layered {
     b200_layered_config c{};
@@ -107,7 +108,7 @@ static void ly_free(b200_plan *p) {
 
 static size_t ly_att_smem(const b200_layer_spec &s, int ring) {
     (void)ring;
-    return (size_t)(s.key_dim + s.window + LY_ATT_THREADS) * 4;
+    return ly::att_smem_floats(s.key_dim, s.window) * 4;
 }
 
 static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
@@ -186,17 +187,16 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
         if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, nullptr, L.P, E, Y.PROJ, nullptr, Y.maxP, 0, &t_proj))) return rc;
         nl++;
         const ly::WindowAttn wa = ly_attn_args(Y, L);
-        if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, st))) return rc;
+        if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st))) return rc;
         nl++;
         const size_t asm_ = ly_att_smem(L.s, Y.ring);
         const bool mma64 = L.s.key_dim == 64 && L.s.value_dim == 64, mma128 = L.s.key_dim == 128 && L.s.value_dim == 128;
-        const bool aligned = Y.maxP % 4 == 0 && L.gd % 2 == 0; // float4 reads of the projection rows, paired stores
-        if (h16 && Y.att_mma && aligned && mma64 && ly::att_mma_smem_bytes<64, 64>(L.s.window) <= (size_t)Y.smem_max)
-            rc = launch_k(p, false, ly::k_window_attention_mma<64, 64>, dim3((n + 63) / 64, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<64, 64>(L.s.window),
-                          (const float *)Y.PROJ, Y.maxP, wa, (const float *)R.kc, (const float *)R.vc, st, n, Y.ATT16, L.gd);
-        else if (h16 && Y.att_mma && aligned && mma128 && ly::att_mma_smem_bytes<128, 128>(L.s.window) <= (size_t)Y.smem_max)
-            rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, dim3((n + 63) / 64, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(L.s.window),
-                          (const float *)Y.PROJ, Y.maxP, wa, (const float *)R.kc, (const float *)R.vc, st, n, Y.ATT16, L.gd);
+        if (h16 && R.kc16 && mma64)
+            rc = launch_k(p, false, ly::k_window_attention_mma<64, 64>, dim3((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<64, 64>(L.s.window),
+                          (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, n, Y.ATT16, L.gd);
+        else if (h16 && R.kc16 && mma128)
+            rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, dim3((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(L.s.window),
+                          (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, n, Y.ATT16, L.gd);
         else if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
                                (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd);
         else rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
@@ -432,6 +432,15 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if ((rc = dalloc(p, &R.vc, (size_t)Y.ring * L.vd * 4))) return rc;
         CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kd * 4));
         CK(cudaMemset(R.vc, 0, (size_t)Y.ring * L.vd * 4));
+        // tensor-core prefill attention: BF16 plans, key = value size 64 or 128, a window whose tiles fit shared memory
+        const bool s64 = L.s.key_dim == 64 && L.s.value_dim == 64, s128 = L.s.key_dim == 128 && L.s.value_dim == 128;
+        const size_t need = s64 ? ly::att_mma_smem_bytes<64, 64>(L.s.window) : ly::att_mma_smem_bytes<128, 128>(L.s.window);
+        if (!Y.f32 && Y.att_mma && Y.cap > 1 && (s64 || s128) && need <= (size_t)Y.smem_max && Y.maxP % 4 == 0) {
+            if ((rc = dalloc(p, &R.kc16, (size_t)Y.ring * L.kd * 2))) return rc;
+            if ((rc = dalloc(p, &R.vc16, (size_t)Y.ring * L.vd * 2))) return rc;
+            CK(cudaMemset(R.kc16, 0, (size_t)Y.ring * L.kd * 2));
+            CK(cudaMemset(R.vc16, 0, (size_t)Y.ring * L.vd * 2));
+        }
     }
     // activations
     Y.logit_rows = Y.cap < 128 ? Y.cap : 128;
