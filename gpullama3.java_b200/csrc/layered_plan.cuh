@@ -139,8 +139,19 @@ static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const 
         if (EPI == ly::EPI_GATED)
             rc = pg::gemm2_persist_launch<pg::GEMM_GATEUP, 256, pg::GEMM2_PERSIST_STAGES_256>(*tc->a, *tc->b, *tc->b2, *tc->c, c16, ldc, n, mt2, N / 128, K, p->n_sms, p->stream, 1,
                                                                                             pg::FLAVOR_BF16 | pg::FLAVOR_GELU_BF16);
-        else if (N % 256 == 0)
-            rc = pg::gemm2_persist_launch<pg::GEMM_F32, 256, pg::GEMM2_PERSIST_STAGES_256>(*tc->a, *tc->b, *tc->b, *tc->c, c32, ldc, n, mt2, N / 256, K, p->n_sms, p->stream, 1, pg::FLAVOR_BF16);
+        else if (N % 256 == 0) {
+            // a narrow output (N = width) leaves most SMs idle: split K over the grid and let every split reduce-add its partial
+            // product into the zeroed result through TMA, as the GGUF prefill does for its residual GEMMs
+            const int ctas = mt2 * (N / 256), nk = K / pg::BK;
+            int sp = p->n_sms / ctas;
+            if (sp > 4) sp = 4;
+            while (sp > 1 && (nk / sp < 8 || (sp - 1) * ((nk + sp - 1) / sp) >= nk)) sp--;
+            if (sp > 1) {
+                if (cudaMemsetAsync(c32, 0, (size_t)n * ldc * 4, p->stream) != cudaSuccess) return fail(p, B200_ERR_CUDA, "cudaMemsetAsync failed");
+                rc = pg::gemm2_launch<pg::GEMM_RESID, 256, pg::GEMM2_STAGES_256>(*tc->a, *tc->b, *tc->b, *tc->c, c32, ldc, n, mt2, N / 256, K, p->stream, sp, pg::FLAVOR_BF16);
+            } else
+                rc = pg::gemm2_persist_launch<pg::GEMM_F32, 256, pg::GEMM2_PERSIST_STAGES_256>(*tc->a, *tc->b, *tc->b, *tc->c, c32, ldc, n, mt2, N / 256, K, p->n_sms, p->stream, 1, pg::FLAVOR_BF16);
+        }
         else
             rc = pg::gemm_launch<pg::GEMM_F32, pg::GEMM_STAGES>(*tc->a, *tc->b, *tc->b, *tc->c, c32, ldc, n, (n + 127) / 128, N / 128, K, p->stream, pg::FLAVOR_BF16);
         return rc ? fail(p, B200_ERR_CUDA, "tensor-core GEMM launch failed (%d)", rc) : B200_OK;
@@ -307,6 +318,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     for (int l = 0; l < c.n_layers; l++) {
         LyLayer &L = Y.layers[l];
         L.s = specs[l];
+        if (L.s.window > c.context_length) L.s.window = c.context_length; // no position is further back than the context: same result, smaller tables
         const b200_layer_spec &s = L.s;
         if (s.mixer != B200_MIXER_WINDOW_ATTENTION) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d", l, s.mixer);
         if (s.heads <= 0 || s.kv_heads <= 0 || s.heads % s.kv_heads || s.key_dim <= 0 || s.value_dim <= 0 || s.window <= 0)
