@@ -396,27 +396,42 @@ __global__ void __launch_bounds__(256) k_qk_prep(float *__restrict__ P, int ldp,
 // One CTA per (row, head): scores of the window into shared memory, softmax with the sink term, weighted value sum, gate.
 // Scores: a group of dk/4 lanes (at most a warp) owns a key and reads its row with coalesced 128-bit loads; values: a group of
 // dv/4 threads owns every groups-th key.  Sizes that are no multiple of 4 take scalar loads.
+// gridDim.z > 1 splits the window of a (row, head) over several CTAs; the last one to arrive merges the parts.
 // Dynamic shared memory: att_smem_floats(dk, window) floats.
 #define LY_ATT_THREADS 256
+// Scratch of a launch that splits every (row, head) over gridDim.z CTAs (the decode step: one row, few heads, many SMs):
+// per part the unnormalised weighted value sum o[dv] and {maximum, sum of exponentials}; count = arrival counter per (row, head).
+struct KeySplit {
+    float *o, *ml;
+    unsigned *count;
+};
 __host__ __device__ inline size_t att_smem_floats(int dk, int window) { return (size_t)((dk + 3) / 4 * 4) + window + 4 * LY_ATT_THREADS; }
 
 template <typename OUT_T>
 __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float *__restrict__ P, int ldp, WindowAttn a, const float *__restrict__ kc,
                                                                      const float *__restrict__ vc, const StepState *__restrict__ st,
-                                                                     OUT_T *__restrict__ out, int ldo) {
+                                                                     OUT_T *__restrict__ out, int ldo, KeySplit ks_) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[32];
+    __shared__ int s_last;
     const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int splits = gridDim.z, z = blockIdx.z;
     const int qd = a.heads * a.dk, kd = a.kv_heads * a.dk, vd = a.kv_heads * a.dv;
     const int g = h / (a.heads / a.kv_heads);
     const int pos = st->pos + r;
-    const int lo = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
-    const int nk = pos - lo + 1;
+    int lo = pos - a.window + 1 > 0 ? pos - a.window + 1 : 0;
+    int nk = pos - lo + 1;
+    if (splits > 1) { // this CTA's share of the window; everything below indexes keys as lo + j, j < nk
+        const int chunk = (nk + splits - 1) / splits, jb = z * chunk;
+        lo += jb;
+        nk = nk - jb < chunk ? nk - jb : chunk;
+        if (nk < 0) nk = 0;
+    }
     float *qs = sm, *sc = sm + (a.dk + 3) / 4 * 4, *part = sc + a.window;
     const float *q = P + (size_t)r * ldp + (size_t)h * a.dk;
     for (int i = tid; i < a.dk; i += LY_ATT_THREADS) qs[i] = q[i];
     __syncthreads();
-    float mx = a.sink ? 0.0f : -INFINITY; // the sink's logit takes part in the maximum
+    float mx = (a.sink && splits == 1) ? 0.0f : -INFINITY; // the sink's logit takes part in the maximum (split runs: when the parts are merged)
     {
         const bool vec = (a.dk & 3) == 0 && (kd & 3) == 0;
         int lpk = 32; // lanes per key
@@ -477,7 +492,9 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
         sum += w;
     }
     sum = block_sum(sum, red); // also orders the sc[] writes before the reads below
-    const float inv = 1.0f / (sum + (a.sink ? expf(-mx) : 0.0f));
+    const float inv = splits > 1 ? 1.0f : 1.0f / (sum + (a.sink ? expf(-mx) : 0.0f)); // split runs keep the unnormalised sum
+    const size_t cell = (size_t)r * a.heads + h; // (row, head)
+    float *my_o = splits > 1 ? ks_.o + (cell * splits + z) * a.dv : nullptr;
     const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * a.dv;
     const int vw = ((a.dv & 3) == 0 && (vd & 3) == 0) ? 4 : 1; // value elements per thread
     int tpk = (a.dv + vw - 1) / vw;                             // threads per key
@@ -505,12 +522,40 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
             for (int e = 0; e < vw; e++) {
                 float o = 0.0f;
                 for (int k = 0; k < groups; k++) o += part[e * LY_ATT_THREADS + k * tpk + dl];
+                if (splits > 1) { my_o[d + e] = o; continue; }
                 o *= inv;
                 if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d + e]));
                 store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d + e, o);
             }
         }
     }
+    if (splits == 1) return;
+    // the last CTA of this (row, head) to arrive merges the parts: maximum over the parts (and the sink), rescaled sums
+    if (tid == 0) { ks_.ml[(cell * splits + z) * 2] = mx; ks_.ml[(cell * splits + z) * 2 + 1] = sum; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(ks_.count + cell, 1u) == (unsigned)splits - 1u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float M = a.sink ? 0.0f : -INFINITY;
+    for (int k = 0; k < splits; k++) M = fmaxf(M, __ldcg(ks_.ml + (cell * splits + k) * 2));
+    float Lsum = a.sink ? expf(-M) : 0.0f;
+    for (int k = 0; k < splits; k++) {
+        const float mk = __ldcg(ks_.ml + (cell * splits + k) * 2);
+        if (mk != -INFINITY) Lsum += __ldcg(ks_.ml + (cell * splits + k) * 2 + 1) * expf(mk - M);
+    }
+    for (int d = tid; d < a.dv; d += LY_ATT_THREADS) {
+        float o = 0.0f;
+        for (int k = 0; k < splits; k++) {
+            const float mk = __ldcg(ks_.ml + (cell * splits + k) * 2);
+            if (mk != -INFINITY) o += __ldcg(ks_.o + (cell * splits + k) * a.dv + d) * expf(mk - M);
+        }
+        o /= Lsum;
+        if (a.gate) o *= 1.0f / (1.0f + expf(-gate[d]));
+        store_out<OUT_T>(out + (size_t)r * ldo + (size_t)h * a.dv + d, o);
+    }
+    if (tid == 0) ks_.count[cell] = 0u; // ready for the next launch
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

@@ -49,6 +49,8 @@ struct Layered {
     StepState *st_pf = nullptr;
     float *trace = nullptr; // [runs][cap][width], allocated on first use
     int smem_max = 0;
+    ly::KeySplit split{nullptr, nullptr, nullptr}; // scratch of the decode attention's key splits (B200_LAYERED_SPLITS=1 turns them off)
+    int max_splits = 8;
     int cap_pad = 1; // rows of the activation buffers: cap, padded to whole 256-row GEMM tiles in BF16 mode
     bool tc = false, tc_head = false;
     bool att_mma = true; // BF16 prefill attention on the tensor cores for key/value sizes 64 and 128 (B200_LAYERED_ATT=simt: the FP32 kernel)
@@ -209,9 +211,14 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
             rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, dim3((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(L.s.window),
                           (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, n, Y.ATT16, L.gd);
         else if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
-                               (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd);
-        else rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
-                           (const float *)R.kc, (const float *)R.vc, st, Y.ATT32, L.gd);
+                               (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd, ly::KeySplit{nullptr, nullptr, nullptr});
+        else {
+            // the decode step has one row and few heads: split every head's window over several CTAs so that the SMs are used
+            int sp = 1;
+            if (decode && Y.split.o && L.s.window >= 64) { sp = p->n_sms / L.s.heads; if (sp > Y.max_splits) sp = Y.max_splits; if (sp < 1) sp = 1; }
+            rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, L.s.heads, sp), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
+                          (const float *)R.kc, (const float *)R.vc, st, Y.ATT32, L.gd, sp > 1 ? Y.split : ly::KeySplit{nullptr, nullptr, nullptr});
+        }
         if (rc) return rc;
         nl++;
         if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.ATT32, Y.ATT16, L.w_o, nullptr, E, L.gd, Y.Y, nullptr, E, 0, &t_o))) return rc;
@@ -474,6 +481,18 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     if ((rc = dalloc(p, &Y.LOG, (size_t)(Y.f32 ? Y.logit_rows : 256) * c.vocab_size * 4))) return rc;
     if ((rc = dalloc(p, &Y.tok, cap * 4))) return rc;
     if ((rc = dalloc(p, &Y.rows, cap * 4))) return rc;
+    {
+        const char *e = getenv("B200_LAYERED_SPLITS");
+        if (e && atoi(e) >= 1) Y.max_splits = atoi(e) > 8 ? 8 : atoi(e);
+        int maxH = 1, maxdv = 1;
+        for (const LyLayer &L : Y.layers) { if (L.s.heads > maxH) maxH = L.s.heads; if (L.s.value_dim > maxdv) maxdv = L.s.value_dim; }
+        if (Y.max_splits > 1) {
+            if ((rc = dalloc(p, &Y.split.o, (size_t)maxH * Y.max_splits * maxdv * 4))) return rc;
+            if ((rc = dalloc(p, &Y.split.ml, (size_t)maxH * Y.max_splits * 2 * 4))) return rc;
+            if ((rc = dalloc(p, &Y.split.count, (size_t)maxH * 4))) return rc;
+            CK(cudaMemset(Y.split.count, 0, (size_t)maxH * 4));
+        }
+    }
     if ((rc = dalloc(p, &Y.st_pf, sizeof(StepState)))) return rc;
     CK(cudaMemset(Y.st_pf, 0, sizeof(StepState)));
     // what the shared single-token entry points use
