@@ -315,3 +315,45 @@ def test_bad_arguments_are_refused(pkg):
     del w["l0.mix.rel"]
     with pytest.raises(Exception):
         make_plan(pkg, cfg, w)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_runner_replays_steps(pkg, tmp_path, dtype):
+    """bin/trace_run on a model directory: steps of many tokens (longer than --chunk, so the runner cuts them), of two tokens
+    and of one token, wanted places out of order, steps that want nothing, two requests one after the other on one plan; the
+    files hold the wanted rows in the order asked, and every step is acknowledged."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    S, O = pkg.synth, oracle()
+    cfg, rows = configs(S)["tiles64"]
+    w = S.pibidra_weights(cfg, 23, bias_rows=rows)
+    mdir = str(tmp_path / "model")
+    S.write_pibidra_dir(mdir, cfg, w)
+    rng = np.random.default_rng(13)
+    reqs = {"a": rng.integers(0, cfg["vocab"], 61).tolist(), "b": rng.integers(0, cfg["vocab"], 9).tolist()}
+    ref = {k: O.forward(cfg, w64(w), v) for k, v in reqs.items()}
+    plan_steps = [("a", 37, [36, 0, 5]), ("a", 2, []), ("a", 20, [19, 18]), ("a", 1, [0]), ("a", 1, []), ("b", 1, [0]), ("b", 8, [7, 3])]
+    lines, expect, at = [], {}, {"a": 0, "b": 0}
+    for n, (rid, count, want) in enumerate(plan_steps):
+        lo = at[rid]
+        at[rid] = lo + count
+        end = [rid] if at[rid] == len(reqs[rid]) else []
+        lines.append(json.dumps({"step": n, "entries": [{"id": rid, "tokens": reqs[rid][lo:lo + count], "want": want}], "end": end}))
+        if want:
+            expect[n] = np.stack([ref[rid][lo + k] for k in want])
+    out = str(tmp_path / "out")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", mdir, "--dtype", dtype, "--out", out, "--max-tokens", "64",
+                        "--chunk", "16"], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == ["done %d" % n for n in range(len(plan_steps))]
+    for n in range(len(plan_steps)):
+        path = os.path.join(out, "%d.f32" % n)
+        if n in expect:
+            got = np.fromfile(path, dtype="<f4").reshape(expect[n].shape)
+            assert_rows(got, expect[n], TOL[dtype], f"step {n}")
+        else:
+            assert not os.path.exists(path)
