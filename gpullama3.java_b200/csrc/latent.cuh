@@ -1,0 +1,243 @@
+// latent.cuh -- device kernels of the layered plans' second family of mechanisms (first user: Latusun), beside those of
+// layered.cuh and sharing its projection and attention kernels:
+//   * k_block_norm_rows  the PARALLEL block's row kernel: x += mult * (a + sum of the feed-forward's per-slot results), then
+//                        TWO norms of the same x (layer norm with weight and bias, one pair per branch) in one pass; also the
+//                        embedding gather and the gathered final norm;
+//   * k_latent_prep      latent attention: RMS norm of the key/value latent, rotation of the shared key part and of every
+//                        head's rotated query part (table-driven: half-split or interleaved pairs, any blend of frequencies),
+//                        cache write [latent | rotated shared key part];
+//   * k_moe_route        sigmoid router in FP32 and selection of the `top` largest scores per row;
+//   * k_moe_group        slots sorted by expert into tiles of 64 for the grouped projection kernels (GemmView);
+//   * k_softcap          x <- cap * tanh(x / cap) over a logits buffer.
+// The latent attention itself runs through k_window_attention: with W_uk folded into the query (q' = W_uk^T q_u per head)
+// and W_uv applied to the attention's output, every head attends over the SAME cached row: keys = [latent | shared key part],
+// values = latent -- one key/value "head" of size rank + dr / rank, never expanded per head.
+// Norm statistics, router, softmax, rotation and the residual sum are FP32.
+#pragma once
+#include "layered.cuh"
+
+namespace ly {
+
+struct BlockNormArgs {
+    float *x;             // [n][E] residual stream
+    const bf16 *emb;      // embedding table [vocab][E]: x = emb_scale * emb[token] (nullable)
+    const int *tokens;    // [n] (nullable: the step's own token)
+    const StepState *st;
+    float emb_scale;
+    const float *add_a;   // [n][E] (nullable): mixer output of the previous layer
+    const float *add_b;   // [n * add_b_terms][E] (nullable): feed-forward results, row r owns entries r * terms .. r * terms + terms - 1
+    int add_b_terms;
+    float add_mult;       // x += add_mult * (a + sum b)
+    float *trace;         // [n][E]: copy of x after the update (nullable)
+    const float *w1, *b1; // first norm (nullable: no output); b nullable
+    float *out1_32;
+    bf16 *out1_16;
+    const float *w2, *b2; // second norm of the same x (nullable)
+    float *out2_32;
+    bf16 *out2_16;
+    const int *gather;    // output row r is computed from x row gather[r] (no update then)
+    int rms;              // 0: (x - mean) / sqrt(var + eps) * w + b;  1: x / sqrt(mean x^2 + eps) * w + b
+    float eps;
+    int E;
+};
+
+__global__ void __launch_bounds__(LY_NORM_THREADS) k_block_norm_rows(BlockNormArgs a) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[32];
+    const int r = blockIdx.x, tid = threadIdx.x, E = a.E;
+    const size_t src = (size_t)(a.gather ? a.gather[r] : r) * E, dst = (size_t)r * E;
+    if (a.emb) {
+        const int token = a.tokens ? a.tokens[r] : a.st->token;
+        const bf16 *e = a.emb + (size_t)token * E;
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = __bfloat162float(e[i]) * a.emb_scale;
+    } else {
+        for (int i = tid; i < E; i += LY_NORM_THREADS) row[i] = a.x[src + i];
+    }
+    if (a.add_a || a.add_b) {
+        for (int i = tid; i < E; i += LY_NORM_THREADS) {
+            float s = a.add_a ? a.add_a[src + i] : 0.0f;
+            for (int k = 0; k < a.add_b_terms; k++) s += a.add_b[((size_t)r * a.add_b_terms + k) * E + i];
+            row[i] = fmaf(a.add_mult, s, row[i]);
+        }
+    }
+    if (!a.gather && (a.emb || a.add_a || a.add_b))
+        for (int i = tid; i < E; i += LY_NORM_THREADS) a.x[src + i] = row[i];
+    if (a.trace)
+        for (int i = tid; i < E; i += LY_NORM_THREADS) a.trace[src + i] = row[i];
+    if (!a.w1 && !a.w2) return;
+    float mean = 0.0f;
+    if (!a.rms) {
+        float s = 0.0f;
+        for (int i = tid; i < E; i += LY_NORM_THREADS) s += row[i];
+        mean = block_sum(s, red) / (float)E;
+    }
+    float ss = 0.0f;
+    for (int i = tid; i < E; i += LY_NORM_THREADS) { const float d = row[i] - mean; ss = fmaf(d, d, ss); }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)E + a.eps);
+    for (int i = tid; i < E; i += LY_NORM_THREADS) {
+        const float u = (row[i] - mean) * inv;
+        if (a.w1) {
+            const float v = fmaf(u, a.w1[i], a.b1 ? a.b1[i] : 0.0f);
+            if (a.out1_32) a.out1_32[dst + i] = v;
+            if (a.out1_16) a.out1_16[dst + i] = __float2bfloat16_rn(v);
+        }
+        if (a.w2) {
+            const float v = fmaf(u, a.w2[i], a.b2 ? a.b2[i] : 0.0f);
+            if (a.out2_32) a.out2_32[dst + i] = v;
+            if (a.out2_16) a.out2_16[dst + i] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Latent attention, the part between the fused projection and the attention kernel.  One CTA per row.
+// Projection row: [q: heads x (dk unrotated | dr rotated)] at q_off, [latent' (rank) | shared key part (dr)] at kv_off.
+// ---------------------------------------------------------------------------------------------------------------------
+struct LatentArgs {
+    int heads, dk, dr, rank;
+    int q_off, kv_off;   // kv_off < 0: the layer reads another layer's cache and writes none
+    const float *cnorm;  // [rank] weight of the latent's RMS norm
+    const float *cs;     // rotation table [positions][rope_dims / 2][2] = (cos, sin), magnitude factor included
+    int rope_dims;       // the first rope_dims entries of a rotated part turn, the rest pass unchanged
+    int rope_layout;     // 0: pair (i, i + rope_dims / 2);  1: pair (2i, 2i + 1)
+    float eps;
+};
+
+__device__ __forceinline__ void rope_pair_index(int i, int dims, int layout, int &u, int &v) {
+    if (layout) { u = 2 * i; v = 2 * i + 1; }
+    else { u = i; v = i + dims / 2; }
+}
+
+// cache [ring][rank + dr];  Q [n][heads * (rank + dr)]: this kernel fills the rotated tail of every head, the folded-key
+// product fills the first rank entries;  qu16 (nullable) [n][heads * dk]: BF16 copy of the unrotated query parts.
+__global__ void __launch_bounds__(256) k_latent_prep(const float *__restrict__ P, int ldp, LatentArgs a, float *__restrict__ cache, int ring,
+                                                     float *__restrict__ Q, bf16 *__restrict__ qu16, const StepState *__restrict__ st) {
+    __shared__ float red[32];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const int pos = st->pos + r, half = a.rope_dims / 2, kw = a.rank + a.dr;
+    const float *p = P + (size_t)r * ldp;
+    const float *cs = a.cs + (size_t)pos * half * 2;
+    if (a.kv_off >= 0) {
+        const float *c = p + a.kv_off, *kr = c + a.rank;
+        float ss = 0.0f;
+        for (int i = tid; i < a.rank; i += 256) ss = fmaf(c[i], c[i], ss);
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)a.rank + a.eps);
+        float *row = cache + (size_t)(pos % ring) * kw;
+        for (int i = tid; i < a.rank; i += 256) row[i] = c[i] * inv * a.cnorm[i];
+        for (int i = tid; i < half; i += 256) {
+            int u, v;
+            rope_pair_index(i, a.rope_dims, a.rope_layout, u, v);
+            const float co = cs[2 * i], si = cs[2 * i + 1];
+            row[a.rank + u] = kr[u] * co - kr[v] * si;
+            row[a.rank + v] = kr[v] * co + kr[u] * si;
+        }
+        for (int i = a.rope_dims + tid; i < a.dr; i += 256) row[a.rank + i] = kr[i];
+    }
+    const int hw = a.dk + a.dr;
+    float *q = Q + (size_t)r * a.heads * kw;
+    for (int e = tid; e < a.heads * half; e += 256) {
+        const int h = e / half, i = e % half;
+        int u, v;
+        rope_pair_index(i, a.rope_dims, a.rope_layout, u, v);
+        const float *qr = p + a.q_off + (size_t)h * hw + a.dk;
+        const float co = cs[2 * i], si = cs[2 * i + 1];
+        q[(size_t)h * kw + a.rank + u] = qr[u] * co - qr[v] * si;
+        q[(size_t)h * kw + a.rank + v] = qr[v] * co + qr[u] * si;
+    }
+    const int rest = a.dr - a.rope_dims;
+    for (int e = tid; e < a.heads * rest; e += 256) {
+        const int h = e / rest, i = a.rope_dims + e % rest;
+        q[(size_t)h * kw + a.rank + i] = p[a.q_off + (size_t)h * hw + a.dk + i];
+    }
+    if (qu16)
+        for (int e = tid; e < a.heads * a.dk; e += 256) {
+            const int h = e / a.dk, d = e % a.dk;
+            qu16[(size_t)r * a.heads * a.dk + e] = __float2bfloat16_rn(p[a.q_off + (size_t)h * hw + d]);
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Mixture of experts: router and grouping.
+// ---------------------------------------------------------------------------------------------------------------------
+// One CTA of four warps per row: scores s_e = sigmoid(<Wr[e], x>) in FP32 (x FP32 or BF16), then the `top` largest (the
+// lowest index wins a tie); ids / wts [n][top], in order of falling score.  Dynamic shared memory: (E + experts) floats.
+template <typename IN_T>
+__global__ void __launch_bounds__(128) k_moe_route(const IN_T *__restrict__ X, const bf16 *__restrict__ Wr, int E, int experts, int top,
+                                                   int *__restrict__ ids, float *__restrict__ wts) {
+    extern __shared__ __align__(16) float sm[];
+    float *xs = sm, *sc = sm + E;
+    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < E; i += 128) xs[i] = (float)X[(size_t)r * E + i];
+    __syncthreads();
+    for (int e = warp; e < experts; e += 4) {
+        const bf16 *w = Wr + (size_t)e * E;
+        float acc = 0.0f;
+        for (int i = lane; i < E; i += 32) acc = fmaf(__bfloat162float(w[i]), xs[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) sc[e] = 1.0f / (1.0f + expf(-acc));
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int k = 0; k < top; k++) {
+            float best = -1.0f;
+            int bi = experts;
+            for (int e = lane; e < experts; e += 32)
+                if (sc[e] > best) { best = sc[e]; bi = e; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+            }
+            if (lane == 0) {
+                ids[(size_t)r * top + k] = bi;
+                wts[(size_t)r * top + k] = best;
+                sc[bi] = -2.0f; // taken
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// One CTA: the slots 0 .. n_slots - 1 (slot = row * top + k, expert ids[slot]) sorted by expert into `perm`, and the list of
+// tiles (at most 64 slots of one expert each) the grouped projections run over; unused tiles get group -1.
+// Dynamic shared memory: 3 * experts ints.
+__global__ void __launch_bounds__(1024) k_moe_group(const int *__restrict__ ids, int n_slots, int experts, int max_tiles, int *__restrict__ perm,
+                                                    int *__restrict__ tile_group, int *__restrict__ tile_row0, int *__restrict__ tile_rows) {
+    extern __shared__ int smi[];
+    int *count = smi, *offs = smi + experts, *cursor = smi + 2 * experts;
+    const int tid = threadIdx.x;
+    for (int e = tid; e < experts; e += 1024) count[e] = cursor[e] = 0;
+    __syncthreads();
+    for (int s = tid; s < n_slots; s += 1024) atomicAdd(&count[ids[s]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int o = 0, t = 0;
+        for (int e = 0; e < experts; e++) {
+            offs[e] = o;
+            for (int b = 0; b < count[e] && t < max_tiles; b += 64, t++) {
+                tile_group[t] = e;
+                tile_row0[t] = o + b;
+                tile_rows[t] = count[e] - b < 64 ? count[e] - b : 64;
+            }
+            o += count[e];
+        }
+        for (; t < max_tiles; t++) { tile_group[t] = -1; tile_row0[t] = 0; tile_rows[t] = 0; }
+    }
+    __syncthreads();
+    // the order of an expert's slots inside `perm` depends on the scheduling; no result does (a row's products are
+    // accumulated in the same order wherever the row sits in its tile)
+    for (int s = tid; s < n_slots; s += 1024) {
+        const int e = ids[s];
+        perm[offs[e] + atomicAdd(&cursor[e], 1)] = s;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_softcap(float *__restrict__ x, long long n, float cap) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+} // namespace ly

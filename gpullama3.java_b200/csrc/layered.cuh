@@ -154,40 +154,117 @@ __device__ __forceinline__ float dot_row_bf16(const bf16 *__restrict__ w, const 
     return warp_sum(acc);
 }
 
+// Optional second grid dimension of a decode projection: blockIdx.y = b selects a per-head operand (offsets b * w_bs / x_bs /
+// y_bs into W, x, y) and, with `group`, the weight matrix of expert group[b] (offset group[b] * w_gs).  in_scale[b] multiplies
+// the INPUT of a gated projection (act(s g) * (s u)); mul multiplies a stored result by sigmoid(mul[b * y_bs + n]).
+struct MvView {
+    long long w_bs, x_bs, y_bs;
+    const int *group;
+    long long w_gs;
+    const float *in_scale;
+    const float *mul;
+};
+
 template <int EPI>
 __global__ void __launch_bounds__(LY_MV_THREADS) k_matvec_bf16(const bf16 *__restrict__ W, const float *__restrict__ bias, const float *__restrict__ x,
-                                                              float *__restrict__ y, int N, int K, int act) {
+                                                              float *__restrict__ y, int N, int K, int act, MvView v_) {
     extern __shared__ __align__(16) float xs[];
+    const int b = blockIdx.y;
+    W += (size_t)b * v_.w_bs + (v_.group ? (size_t)v_.group[b] * v_.w_gs : (size_t)0);
+    x += (size_t)b * v_.x_bs;
+    y += (size_t)b * v_.y_bs;
+    const float sc = v_.in_scale ? v_.in_scale[b] : 1.0f;
     for (int i = threadIdx.x; i < K; i += LY_MV_THREADS) xs[i] = x[i];
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const bool vec = (K & 7) == 0;
+    const bool vec = (K & 7) == 0 && (((size_t)W) & 15) == 0;
     for (int n = blockIdx.x * (LY_MV_THREADS / 32) + warp; n < N; n += gridDim.x * (LY_MV_THREADS / 32)) {
         float v = dot_row_bf16(W + (size_t)n * K, xs, K, lane, vec);
         if (EPI == EPI_GATED) {
             const float u = dot_row_bf16(W + (size_t)(N + n) * K, xs, K, lane, vec);
-            v = act_apply(act, v) * u;
-        } else if (bias) v += bias[n];
+            v = act_apply(act, v * sc) * (u * sc);
+        } else {
+            if (bias) v += bias[n];
+            if (v_.mul) v *= 1.0f / (1.0f + expf(-v_.mul[(size_t)b * v_.y_bs + n]));
+        }
         if (lane == 0) y[n] = v;
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Views of a prefill projection's operands, shared by the FP32 and the tensor-core kernel.  All optional (zero = plain GEMM):
+//   * lda: row stride of A when A is a column block of a wider buffer;
+//   * blockIdx.z batches (per-head products): column offset z * a_bs into an A row, element offset z * w_bs into W, column
+//     offset z * c_bs into a C row;
+//   * grouped rows (mixture of experts): blockIdx.y is a TILE of at most 64 entries of `perm`, a list of slots sorted by
+//     group; tile t belongs to group tile_group[t] (-1: nothing to do) whose weight matrix starts at tile_group[t] * w_gs,
+//     and covers perm[tile_row0[t] .. + tile_rows[t]).  A slot s reads A row s / a_div and writes C row s.  in_scale[s]
+//     multiplies the INPUT of a gated projection: act(sc g) * (sc u);
+//   * mul: a stored result is multiplied by sigmoid(mul[row][z * c_bs + n]) (an output gate).
+// ---------------------------------------------------------------------------------------------------------------------
+struct GemmView {
+    int lda;
+    long long a_bs, w_bs, c_bs;
+    const int *tile_group, *tile_row0, *tile_rows, *perm;
+    int a_div;
+    long long w_gs;
+    const float *in_scale;
+    const float *mul;
+    int ldmul;
+};
+
+// Fills the A / C row numbers of this CTA's 64 rows (-1: outside); returns false when the tile has no work.
+__device__ __forceinline__ bool gemm_rows(const GemmView &g, int M, int *s_arow, int *s_crow, int tid, int nthreads) {
+    if (g.tile_group) {
+        const int t = blockIdx.y;
+        if (g.tile_group[t] < 0) return false;
+        const int r0 = g.tile_row0[t], nr = g.tile_rows[t];
+        for (int r = tid; r < 64; r += nthreads) {
+            const int slot = r < nr ? g.perm[r0 + r] : -1;
+            s_crow[r] = slot;
+            s_arow[r] = slot < 0 ? -1 : slot / g.a_div;
+        }
+    } else {
+        const int m0 = blockIdx.y * 64;
+        for (int r = tid; r < 64; r += nthreads) s_arow[r] = s_crow[r] = m0 + r < M ? m0 + r : -1;
+    }
+    return true;
+}
+
+template <typename T> __device__ __forceinline__ void store_out(T *p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int EPI>
+__device__ __forceinline__ float gemm_epilogue(const GemmView &g, float a0, float a1, const float *bias, int crow, int n, long long c_off, int act) {
+    if (EPI == EPI_GATED) {
+        const float sc = g.in_scale ? g.in_scale[crow] : 1.0f;
+        return act_apply(act, a0 * sc) * (a1 * sc);
+    }
+    float v = a0 + (bias ? bias[n] : 0.0f);
+    if (g.mul) v *= 1.0f / (1.0f + expf(-g.mul[(size_t)crow * g.ldmul + c_off + n]));
+    return v;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Prefill projection in true FP32 (no tensor cores): C[M][N] = A[M][K] W[N][K]^T.  64 x 64 x 16 tiles, 4 x 4 per thread.
 // OUT_T = float or bf16 (the gated epilogue feeds the next GEMM).
 // ---------------------------------------------------------------------------------------------------------------------
-template <typename T> __device__ __forceinline__ void store_out(T *p, float v);
-template <> __device__ __forceinline__ void store_out<float>(float *p, float v) { *p = v; }
-template <> __device__ __forceinline__ void store_out<bf16>(bf16 *p, float v) { *p = __float2bfloat16_rn(v); }
-
 template <int EPI, typename OUT_T>
 __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, const bf16 *__restrict__ W, const float *__restrict__ bias,
-                                                   OUT_T *__restrict__ C, int M, int N, int K, int ldc, int act) {
+                                                   OUT_T *__restrict__ C, int M, int N, int K, int ldc, int act, GemmView g) {
     constexpr int BM = 64, BN = 64, BK = 16, NB = EPI == EPI_GATED ? 2 : 1;
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[NB][BK][BN + 4];
+    __shared__ int s_arow[64], s_crow[64];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int n0 = blockIdx.x * BN;
+    if (!gemm_rows(g, M, s_arow, s_crow, tid, 256)) return;
+    const int lda = g.lda ? g.lda : K;
+    const long long c_off = (long long)blockIdx.z * g.c_bs;
+    A += (size_t)blockIdx.z * g.a_bs;
+    W += (size_t)blockIdx.z * g.w_bs + (g.tile_group ? (size_t)g.tile_group[blockIdx.y] * g.w_gs : (size_t)0);
+    __syncthreads();
     float acc[NB][4][4];
 #pragma unroll
     for (int b = 0; b < NB; b++)
@@ -198,8 +275,8 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
     for (int k0 = 0; k0 < K; k0 += BK) {
         for (int e = tid; e < BM * BK; e += 256) {
             const int r = e / BK, c = e % BK;
-            const int m = m0 + r, k = k0 + c;
-            As[c][r] = (m < M && k < K) ? A[(size_t)m * K + k] : 0.0f;
+            const int m = s_arow[r], k = k0 + c;
+            As[c][r] = (m >= 0 && k < K) ? A[(size_t)m * lda + k] : 0.0f;
         }
 #pragma unroll
         for (int b = 0; b < NB; b++)
@@ -229,16 +306,13 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const int m = m0 + ty * 4 + i;
-        if (m >= M) continue;
+        const int m = s_crow[ty * 4 + i];
+        if (m < 0) continue;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
-            float v;
-            if (EPI == EPI_GATED) v = act_apply(act, acc[0][i][j]) * acc[NB - 1][i][j];
-            else v = acc[0][i][j] + (bias ? bias[n] : 0.0f);
-            store_out<OUT_T>(C + (size_t)m * ldc + n, v);
+            store_out<OUT_T>(C + (size_t)m * ldc + c_off + n, gemm_epilogue<EPI>(g, acc[0][i][j], acc[NB - 1][i][j], bias, m, n, c_off, act));
         }
     }
 }
@@ -254,34 +328,46 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// rows x 32 BF16 tile of a row-major [R][K] matrix into shared memory (stride 40 elements), zero-filled outside
-__device__ __forceinline__ void load_tile_bf16(bf16 (*dst)[40], const bf16 *__restrict__ src, int r0, int R, int k0, int K, bool vec, int tid, int nthreads) {
+// 64 x 32 BF16 tile of a row-major matrix (row stride ld) into shared memory (stride 40 elements), zero-filled outside.
+// rowmap (shared memory, nullable) names the source row of every tile row (-1: none); without it tile row r is row r0 + r < R.
+__device__ __forceinline__ void load_tile_bf16(bf16 (*dst)[40], const bf16 *__restrict__ src, int r0, int R, const int *rowmap, int ld, int k0, int K, bool vec,
+                                               int tid, int nthreads) {
     if (vec) { // 4 chunks of 8 elements per row
         for (int e = tid; e < 64 * 4; e += nthreads) {
             const int r = e >> 2, c = (e & 3) * 8;
+            const int row = rowmap ? rowmap[r] : (r0 + r < R ? r0 + r : -1);
             int4 v = make_int4(0, 0, 0, 0);
-            if (r0 + r < R && k0 + c < K) v = *reinterpret_cast<const int4 *>(src + (size_t)(r0 + r) * K + k0 + c);
+            if (row >= 0 && k0 + c < K) v = *reinterpret_cast<const int4 *>(src + (size_t)row * ld + k0 + c);
             *reinterpret_cast<int4 *>(&dst[r][c]) = v;
         }
     } else {
         for (int e = tid; e < 64 * 32; e += nthreads) {
             const int r = e >> 5, c = e & 31;
-            dst[r][c] = (r0 + r < R && k0 + c < K) ? src[(size_t)(r0 + r) * K + k0 + c] : __float2bfloat16_rn(0.0f);
+            const int row = rowmap ? rowmap[r] : (r0 + r < R ? r0 + r : -1);
+            dst[r][c] = (row >= 0 && k0 + c < K) ? src[(size_t)row * ld + k0 + c] : __float2bfloat16_rn(0.0f);
         }
     }
 }
 
 template <int EPI, typename OUT_T>
 __global__ void __launch_bounds__(128) k_gemm_bf16(const bf16 *__restrict__ A, const bf16 *__restrict__ W, const float *__restrict__ bias,
-                                                    OUT_T *__restrict__ C, int M, int N, int K, int ldc, int act) {
+                                                    OUT_T *__restrict__ C, int M, int N, int K, int ldc, int act, GemmView gv) {
     constexpr int NB = EPI == EPI_GATED ? 2 : 1;
     __shared__ __align__(16) bf16 As[64][40];
     __shared__ __align__(16) bf16 Bs[NB][64][40];
+    __shared__ int s_arow[64], s_crow[64];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
     const int g = lane >> 2, t = lane & 3;
-    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
-    const bool vec = (K & 7) == 0;
+    const int n0 = blockIdx.x * 64;
+    if (!gemm_rows(gv, M, s_arow, s_crow, tid, 128)) return;
+    const int lda = gv.lda ? gv.lda : K;
+    const long long c_off = (long long)blockIdx.z * gv.c_bs;
+    A += (size_t)blockIdx.z * gv.a_bs;
+    W += (size_t)blockIdx.z * gv.w_bs + (gv.tile_group ? (size_t)gv.tile_group[blockIdx.y] * gv.w_gs : (size_t)0);
+    const bool vecA = (K & 7) == 0 && (lda & 7) == 0 && (((size_t)A) & 15) == 0;
+    const bool vecW = (K & 7) == 0 && (((size_t)W) & 15) == 0;
+    __syncthreads();
     float acc[NB][2][4][4];
 #pragma unroll
     for (int b = 0; b < NB; b++)
@@ -292,9 +378,9 @@ __global__ void __launch_bounds__(128) k_gemm_bf16(const bf16 *__restrict__ A, c
 #pragma unroll
                 for (int e = 0; e < 4; e++) acc[b][i][j][e] = 0.0f;
     for (int k0 = 0; k0 < K; k0 += 32) {
-        load_tile_bf16(As, A, m0, M, k0, K, vec, tid, 128);
+        load_tile_bf16(As, A, 0, 0, s_arow, lda, k0, K, vecA, tid, 128);
 #pragma unroll
-        for (int b = 0; b < NB; b++) load_tile_bf16(Bs[b], W + (size_t)b * N * K, n0, N, k0, K, vec, tid, 128);
+        for (int b = 0; b < NB; b++) load_tile_bf16(Bs[b], W + (size_t)b * N * K, n0, N, nullptr, K, k0, K, vecW, tid, 128);
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < 32; kk += 16) {
@@ -327,13 +413,10 @@ __global__ void __launch_bounds__(128) k_gemm_bf16(const bf16 *__restrict__ A, c
         for (int j = 0; j < 4; j++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const int m = m0 + wm + i * 16 + g + (e >> 1) * 8;
+                const int m = s_crow[wm + i * 16 + g + (e >> 1) * 8];
                 const int n = n0 + wn + j * 8 + 2 * t + (e & 1);
-                if (m >= M || n >= N) continue;
-                float v;
-                if (EPI == EPI_GATED) v = act_apply(act, acc[0][i][j][e]) * acc[NB - 1][i][j][e];
-                else v = acc[0][i][j][e] + (bias ? bias[n] : 0.0f);
-                store_out<OUT_T>(C + (size_t)m * ldc + n, v);
+                if (m < 0 || n >= N) continue;
+                store_out<OUT_T>(C + (size_t)m * ldc + c_off + n, gemm_epilogue<EPI>(gv, acc[0][i][j][e], acc[NB - 1][i][j][e], bias, m, n, c_off, act));
             }
 }
 
@@ -344,6 +427,8 @@ struct WindowAttn {
     int heads, kv_heads, dk, dv; // query heads, key/value heads, key size, value size
     int window;                  // position i sees j with 0 <= i - j < window
     int ring;                    // cache slots: position j lives in slot j % ring (ring >= window - 1 + rows of a step)
+    int ldk, ldv;                // row strides of the key and the value cache (kv_heads * dk, kv_heads * dv when each has rows of its own; a
+                                 // latent cache serves both from one row: keys = the whole row, values = its first dv entries)
     int bias_rows;               // rows of the distance table rel[bias_rows][heads]
     float scale, softcap;        // e = softcap * tanh(scale * <q, k> / softcap) + rel[bucket[i - j]][h]   (softcap <= 0: no cap)
     const float *rel;            // [bias_rows][heads] (nullable: no distance bias)
@@ -433,7 +518,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     __syncthreads();
     float mx = (a.sink && splits == 1) ? 0.0f : -INFINITY; // the sink's logit takes part in the maximum (split runs: when the parts are merged)
     {
-        const bool vec = (a.dk & 3) == 0 && (kd & 3) == 0;
+        const bool vec = (a.dk & 3) == 0 && (a.ldk & 3) == 0;
         int lpk = 32; // lanes per key
         if (vec) { lpk = 1; while (lpk < a.dk / 4 && lpk < 32) lpk <<= 1; }
         const int kpw = 32 / lpk, sub = lane % lpk, ks = lane / lpk;
@@ -454,7 +539,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
                 for (int u = 0; u < 4; u++) {
                     const int j = j0 + u * stride + ks;
                     kv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (has && j < nk) kv[u] = *reinterpret_cast<const float4 *>(kc + (size_t)((lo + j) % a.ring) * kd + (size_t)g * a.dk + 4 * sub);
+                    if (has && j < nk) kv[u] = *reinterpret_cast<const float4 *>(kc + (size_t)((lo + j) % a.ring) * a.ldk + (size_t)g * a.dk + 4 * sub);
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
@@ -469,7 +554,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
                 const int j = j0 + ks;
                 float d = 0.0f;
                 if (j < nk) {
-                    const float *kr = kc + (size_t)((lo + j) % a.ring) * kd + (size_t)g * a.dk;
+                    const float *kr = kc + (size_t)((lo + j) % a.ring) * a.ldk + (size_t)g * a.dk;
                     if (vec) {
                         for (int c = sub; c < a.dk / 4; c += lpk) {
                             const float4 kv = *reinterpret_cast<const float4 *>(kr + 4 * c), qv = *reinterpret_cast<const float4 *>(qs + 4 * c);
@@ -496,7 +581,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     const size_t cell = (size_t)r * a.heads + h; // (row, head)
     float *my_o = splits > 1 ? ks_.o + (cell * splits + z) * a.dv : nullptr;
     const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * a.dv;
-    const int vw = ((a.dv & 3) == 0 && (vd & 3) == 0) ? 4 : 1; // value elements per thread
+    const int vw = ((a.dv & 3) == 0 && (a.ldv & 3) == 0) ? 4 : 1; // value elements per thread
     int tpk = (a.dv + vw - 1) / vw;                             // threads per key
     if (tpk > LY_ATT_THREADS) tpk = LY_ATT_THREADS;
     const int groups = LY_ATT_THREADS / tpk, grp = tid / tpk, dl = tid % tpk;
@@ -506,7 +591,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
         if (grp < groups && d < a.dv) {
 #pragma unroll 4
             for (int j = grp; j < nk; j += groups) {
-                const float *vr = vc + (size_t)((lo + j) % a.ring) * vd + (size_t)g * a.dv + d;
+                const float *vr = vc + (size_t)((lo + j) % a.ring) * a.ldv + (size_t)g * a.dv + d;
                 const float w = sc[j];
                 if (vw == 4) {
                     const float4 v = *reinterpret_cast<const float4 *>(vr);

@@ -14,8 +14,12 @@
 // prefill: n rows per launch): norm (post-norm + residual of the previous sublayer, pass prologue, pre-norm) -> fused
 // q|k|v|gate projection (+bias) -> whole-projection q/k norm + ring write -> window attention (+gate) -> output projection ->
 // norm -> gated feed-forward projection (activation in the epilogue) -> down projection.
+//
+// Two block kinds share the plan: the sandwich block above (B200_BLOCK_SANDWICH) and the parallel block of latent_plan.cuh
+// (B200_BLOCK_PARALLEL: latent attention and a mixture of experts reading two norms of the same residual row).
 #pragma once
 #include "layered.cuh"
+#include "latent.cuh"
 
 struct LyLayer {
     b200_layer_spec s{};
@@ -24,6 +28,16 @@ struct LyLayer {
     float *b_proj = nullptr;
     float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *qnorm = nullptr, *knorm = nullptr, *rel = nullptr;
     int *bucket = nullptr;
+    // latent attention (B200_MIXER_LATENT_ATTENTION): columns of q, [latent' | shared key part] and gate in a projection row; cache row
+    // kw = kv_rank + rot_dim; folded query row qw = heads * kw; attention output in latent space lw = heads * kv_rank
+    int q_off = 0, kv_off = -1, g_off = -1, kw = 0, qw = 0, lw = 0;
+    ly::bf16 *w_ukT = nullptr, *w_uv = nullptr; // [heads][kv_rank][key_dim] (W_uk transposed per head at upload), [heads][value_dim][kv_rank]
+    float *cnorm = nullptr;
+    const float *rope = nullptr;                // [context][rope_dims / 2][2], shared between layers with the same rotation
+    // parallel block: biases of the two layer norms; mixture of experts: router [experts][width], w_gu = [experts][2 ff][width],
+    // w_down = [experts][width][ff]
+    float *ln1_b = nullptr, *ln2_b = nullptr;
+    ly::bf16 *w_router = nullptr;
     // TMA descriptors of the tensor-core prefill (BF16 compute mode, shapes the tcgen05 GEMM tiles cover); *_ok = usable
     CUtensorMap m_proj, m_o, m_gate, m_up, m_down, m_att, m_h;
     bool tc_proj = false, tc_o = false, tc_gu = false, tc_down = false;
@@ -33,6 +47,8 @@ struct LyRun {
     bool first = false; // first layer of a loop pass
     float *kc = nullptr, *vc = nullptr;
     ly::bf16 *kc16 = nullptr, *vc16 = nullptr; // BF16 twin rows (BF16 plans whose head sizes the tensor-core attention takes)
+    int kw = 0, vw = 0;                        // floats per cache row (latent attention: one cache, kw = kv_rank + rot_dim, vc == nullptr)
+    bool own = true;                           // false: kc is the cache of the run this layer reads (kv_from)
 };
 struct Layered {
     b200_layered_config c{};
@@ -55,6 +71,13 @@ struct Layered {
     bool tc = false, tc_head = false;
     bool att_mma = true; // BF16 prefill attention on the tensor cores for key/value sizes 64 and 128 (B200_LAYERED_ATT=simt: the FP32 kernel)
     CUtensorMap m_a, m_head, m_proj_c, m_y_c, m_log_c;
+    // parallel block / latent attention / mixture of experts
+    float *final_norm_b = nullptr;
+    float *A2_32 = nullptr, *Q = nullptr, *LAT32 = nullptr, *YS = nullptr, *moe_wts = nullptr;
+    ly::bf16 *A2_16 = nullptr, *QU16 = nullptr, *LAT16 = nullptr;
+    int *moe_ids = nullptr, *moe_perm = nullptr, *tile_group = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr;
+    int maxQ = 0, maxL = 0, maxQU = 0, maxTop = 0, maxExperts = 0, max_tiles = 0, max_att_dv = 1;
+    std::vector<std::pair<std::vector<float>, float *>> rope_tables; // (key, device table)
 };
 
 // What ly_project needs to take the tcgen05 route: operand and result descriptors (nullptr = CUDA-core / mma.sync kernels).
@@ -108,15 +131,18 @@ static void ly_free(b200_plan *p) {
     p->ly = nullptr;
 }
 
+static size_t ly_att_smem(int dk, int window) { return ly::att_smem_floats(dk, window) * 4; }
 static size_t ly_att_smem(const b200_layer_spec &s, int ring) {
     (void)ring;
-    return ly::att_smem_floats(s.key_dim, s.window) * 4;
+    // latent attention attends over the cached row [latent | shared key part] with one key/value head
+    return ly_att_smem(s.mixer == B200_MIXER_LATENT_ATTENTION ? s.kv_rank + s.rot_dim : s.key_dim, s.window);
 }
 
 static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
     ly::WindowAttn a{};
     a.heads = L.s.heads; a.kv_heads = L.s.kv_heads; a.dk = L.s.key_dim; a.dv = L.s.value_dim;
     a.window = L.s.window; a.ring = Y.ring; a.bias_rows = L.s.bias_rows;
+    a.ldk = L.kd; a.ldv = L.vd;
     a.scale = L.s.score_scale; a.softcap = L.s.softcap;
     a.rel = L.rel; a.bucket = L.bucket; a.qnorm = L.qnorm; a.knorm = L.knorm;
     a.sink = L.s.sink; a.gate = L.s.gate; a.eps = Y.c.norm_eps;
@@ -133,7 +159,7 @@ static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const 
     if (decode) {
         const int warps = LY_MV_THREADS / 32;
         int grid = (N + warps - 1) / warps;
-        return launch_k(p, false, ly::k_matvec_bf16<EPI>, dim3(grid), dim3(LY_MV_THREADS), (size_t)K * 4, W, bias, a32, c32, N, K, act);
+        return launch_k(p, false, ly::k_matvec_bf16<EPI>, dim3(grid), dim3(LY_MV_THREADS), (size_t)K * 4, W, bias, a32, c32, N, K, act, ly::MvView{});
     }
     if (tc && tc->a && !Y.f32) {
         const int mt2 = (n + 255) / 256 * 2;
@@ -159,15 +185,18 @@ static int ly_project(b200_plan *p, bool decode, int n, const float *a32, const 
         return rc ? fail(p, B200_ERR_CUDA, "tensor-core GEMM launch failed (%d)", rc) : B200_OK;
     }
     dim3 grid((N + 63) / 64, (n + 63) / 64);
-    if (Y.f32) return launch_k(p, false, ly::k_gemm_f32<EPI, float>, grid, dim3(256), (size_t)0, a32, W, bias, c32, n, N, K, ldc, act);
-    if (c16) return launch_k(p, false, ly::k_gemm_bf16<EPI, ly::bf16>, grid, dim3(128), (size_t)0, a16, W, bias, c16, n, N, K, ldc, act);
-    return launch_k(p, false, ly::k_gemm_bf16<EPI, float>, grid, dim3(128), (size_t)0, a16, W, bias, c32, n, N, K, ldc, act);
+    if (Y.f32) return launch_k(p, false, ly::k_gemm_f32<EPI, float>, grid, dim3(256), (size_t)0, a32, W, bias, c32, n, N, K, ldc, act, ly::GemmView{});
+    if (c16) return launch_k(p, false, ly::k_gemm_bf16<EPI, ly::bf16>, grid, dim3(128), (size_t)0, a16, W, bias, c16, n, N, K, ldc, act, ly::GemmView{});
+    return launch_k(p, false, ly::k_gemm_bf16<EPI, float>, grid, dim3(128), (size_t)0, a16, W, bias, c32, n, N, K, ldc, act, ly::GemmView{});
 }
+
+#include "latent_plan.cuh"
 
 // Enqueue the forward of n rows on p->stream.  decode: the single-token step (row 0, position and token from *st).
 // with_head (decode only): final norm + classifier into p->logits.  Prefill leaves the finished residual rows in X.
 static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, const int *tokens, bool with_head, float *trace, int *launches) {
     Layered &Y = *p->ly;
+    if (Y.c.block == B200_BLOCK_PARALLEL) return ly_enqueue_parallel(p, decode, n, st, tokens, with_head, trace, launches);
     const int E = Y.c.width;
     const bool h16 = !decode && !Y.f32; // prefill in BF16 mode rounds GEMM operands to BF16
     int nl = 0, rc;
@@ -280,7 +309,7 @@ static int ly_tc_init(b200_plan *p) {
         const int F = L.s.ff_dim;
         L.tc_proj = fits(L.P, E) && Y.maxP % 4 == 0 && pg::make_map(&L.m_proj, L.w_proj, L.P, E, 128) == 0;
         L.tc_o = fits(E, L.gd) && pg::make_map(&L.m_o, L.w_o, E, L.gd, 128) == 0 && pg::make_map(&L.m_att, Y.ATT16, rows, L.gd, pg::BM) == 0;
-        if (L.w_gu) {
+        if (L.w_gu && L.s.ff_kind == B200_FF_DENSE_GATED) {
             L.tc_gu = fits(F, E) && L.s.ff_act == B200_ACT_GELU_TANH && pg::make_map(&L.m_gate, L.w_gu, F, E, 128) == 0 &&
                       pg::make_map(&L.m_up, L.w_gu + (size_t)F * E, F, E, 128) == 0;
             L.tc_down = fits(E, F) && pg::make_map(&L.m_down, L.w_down, E, F, 128) == 0 && pg::make_map(&L.m_h, Y.H16, rows, F, pg::BM) == 0;
@@ -297,11 +326,15 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     Layered &Y = *Yp;
     Y.c = *cfg;
     const b200_layered_config &c = Y.c;
-    if (c.arch != B200_ARCH_PIBIDRA) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
+    if (c.arch != B200_ARCH_PIBIDRA && c.arch != B200_ARCH_LATUSUN) return fail(p, B200_ERR_UNSUPPORTED, "unknown layered arch %d", c.arch);
+    if (c.block != B200_BLOCK_SANDWICH && c.block != B200_BLOCK_PARALLEL) return fail(p, B200_ERR_BAD_ARG, "unknown block kind %d", c.block);
+    const bool par = c.block == B200_BLOCK_PARALLEL;
+    if (par && Y.has_loop && c.loop_stop > c.loop_start) return fail(p, B200_ERR_UNSUPPORTED, "parallel blocks do not loop");
     if (c.width <= 0 || c.vocab_size <= 0 || c.n_layers <= 0 || c.context_length <= 0) return fail(p, B200_ERR_BAD_ARG, "width, vocabulary, layers and context must be positive");
     if (c.compute != B200_COMPUTE_BF16 && c.compute != B200_COMPUTE_F32) return fail(p, B200_ERR_BAD_ARG, "compute must be B200_COMPUTE_BF16 or B200_COMPUTE_F32");
     Y.f32 = c.compute == B200_COMPUTE_F32;
     Y.has_loop = c.loop_times >= 0;
+    if (Y.c.block == B200_BLOCK_PARALLEL && !(Y.c.residual_mult == Y.c.residual_mult)) return fail(p, B200_ERR_BAD_ARG, "residual multiplier is not a number");
     { const char *e = getenv("B200_LAYERED_ATT"); Y.att_mma = !(e && e[0] == 's'); }
     if (Y.has_loop && (c.loop_start < 0 || c.loop_stop > c.n_layers || c.loop_start > c.loop_stop)) return fail(p, B200_ERR_BAD_ARG, "loop [%d, %d) outside the %d layers", c.loop_start, c.loop_stop, c.n_layers);
     const int E = c.width;
@@ -327,6 +360,28 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         L.s = specs[l];
         if (L.s.window > c.context_length) L.s.window = c.context_length; // no position is further back than the context: same result, smaller tables
         const b200_layer_spec &s = L.s;
+        if (par) {
+            // parallel block: latent attention and a mixture of experts (or no feed-forward)
+            if (s.mixer != B200_MIXER_LATENT_ATTENTION) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d in a parallel block", l, s.mixer);
+            L.s.window = c.context_length; // causal over the whole sequence
+            if ((rc = ly_latent_sizes(p, l, L, c.n_layers, specs))) return rc;
+            if (s.ff_kind != B200_FF_NONE && s.ff_kind != B200_FF_MOE) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: feed-forward kind %d in a parallel block", l, s.ff_kind);
+            if (s.ff_kind == B200_FF_MOE) {
+                if (s.ff_dim <= 0 || s.ff_experts <= 0 || s.ff_top <= 0 || s.ff_top > s.ff_experts || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU))
+                    return fail(p, B200_ERR_BAD_ARG, "layer %d: %d experts of width %d, %d chosen, activation %d", l, s.ff_experts, s.ff_dim, s.ff_top, s.ff_act);
+                if (s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
+                if (s.ff_top > Y.maxTop) Y.maxTop = s.ff_top;
+                if (s.ff_experts > Y.maxExperts) Y.maxExperts = s.ff_experts;
+            }
+            if (L.P > Y.maxP) Y.maxP = L.P;
+            if (L.gd > Y.maxO) Y.maxO = L.gd;
+            if (L.qw > Y.maxQ) Y.maxQ = L.qw;
+            if (L.lw > Y.maxL) Y.maxL = L.lw;
+            if (s.heads * s.key_dim > Y.maxQU) Y.maxQU = s.heads * s.key_dim;
+            if (s.kv_rank > Y.max_att_dv) Y.max_att_dv = s.kv_rank;
+            if (L.s.window > Y.max_window) Y.max_window = L.s.window;
+            continue;
+        }
         if (s.mixer != B200_MIXER_WINDOW_ATTENTION) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: mixer %d", l, s.mixer);
         if (s.heads <= 0 || s.kv_heads <= 0 || s.heads % s.kv_heads || s.key_dim <= 0 || s.value_dim <= 0 || s.window <= 0)
             return fail(p, B200_ERR_BAD_ARG, "layer %d: heads %d / kv heads %d / key %d / value %d / window %d", l, s.heads, s.kv_heads, s.key_dim, s.value_dim, s.window);
@@ -341,16 +396,21 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (L.gd > Y.maxO) Y.maxO = L.gd;
         if (s.ff_kind == B200_FF_DENSE_GATED && s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
         if (s.window > Y.max_window) Y.max_window = s.window;
+        if (s.value_dim > Y.max_att_dv) Y.max_att_dv = s.value_dim;
     }
     {
         int maxK = E > Y.maxO ? E : Y.maxO;
         if (Y.maxF > maxK) maxK = Y.maxF;
+        for (const LyLayer &L : Y.layers) if (L.s.kv_rank > maxK) maxK = L.s.kv_rank; // reduction width of the per-head value expansion
         size_t need = (size_t)maxK * 4;
         for (const LyLayer &L : Y.layers) if (ly_att_smem(L.s, 0) > need) need = ly_att_smem(L.s, 0);
         if (need > (size_t)Y.smem_max) return fail(p, B200_ERR_UNSUPPORTED, "a row of %zu bytes (widest activation or window) exceeds the %d bytes of shared memory a CTA can hold", need, Y.smem_max);
         static bool attrs = false; // per function and process-wide, like plan.cu's set_smem_attrs
         if (!attrs) {
             CK(set_max_dyn(ly::k_norm_rows, Y.smem_max));
+            CK(set_max_dyn(ly::k_block_norm_rows, Y.smem_max));
+            CK(set_max_dyn(ly::k_moe_route<float>, Y.smem_max));
+            CK(set_max_dyn(ly::k_moe_route<ly::bf16>, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_STORE>, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_GATED>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention<float>, Y.smem_max));
@@ -386,12 +446,17 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     if ((rc = dalloc(p, &Y.head, (size_t)c.vocab_size * E * 2))) return rc;
     if ((rc = ly_mat(p, tensors, nt, "head", c.vocab_size, E, Y.head, 0))) return rc;
     if ((rc = ly_vec_f32(p, tensors, nt, "final.norm", E, &Y.final_norm))) return rc;
+    if (par && (rc = ly_vec_f32(p, tensors, nt, "final.norm.b", E, &Y.final_norm_b))) return rc;
     if (Y.has_loop && c.loop_times > 0)
         if ((rc = ly_vec_f32(p, tensors, nt, "loop.step", (int64_t)c.loop_times * E, &Y.step))) return rc;
     for (int l = 0; l < c.n_layers; l++) {
         LyLayer &L = Y.layers[l];
         const b200_layer_spec &s = L.s;
         const std::string pre = "l" + std::to_string(l) + ".", mx = pre + "mix.", ff = pre + "mlp.";
+        if (par) {
+            if ((rc = ly_latent_upload(p, l, L, tensors, nt))) return rc;
+            continue;
+        }
         if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1", E, &L.norm1))) return rc;
         if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1b", E, &L.norm1b))) return rc;
         if ((rc = dalloc(p, &L.w_proj, (size_t)L.P * E * 2))) return rc;
@@ -447,6 +512,15 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     // per-run rings
     for (LyRun &R : Y.runs) {
         const LyLayer &L = Y.layers[R.layer];
+        if (L.s.mixer == B200_MIXER_LATENT_ATTENTION) {
+            // one cache of [latent | rotated shared key part] rows; a layer that reads another layer's cache points at it (runs = layers here)
+            R.kw = L.kw;
+            if (L.s.kv_from >= 0) { R.own = false; R.kc = Y.runs[L.s.kv_from].kc; continue; }
+            if ((rc = dalloc(p, &R.kc, (size_t)Y.ring * L.kw * 4))) return rc;
+            CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kw * 4));
+            continue;
+        }
+        R.kw = L.kd; R.vw = L.vd;
         if ((rc = dalloc(p, &R.kc, (size_t)Y.ring * L.kd * 4))) return rc;
         if ((rc = dalloc(p, &R.vc, (size_t)Y.ring * L.vd * 4))) return rc;
         CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kd * 4));
@@ -466,17 +540,40 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     Y.cap_pad = Y.f32 ? Y.cap : (Y.cap + 255) / 256 * 256;
     const size_t cap = (size_t)Y.cap_pad, rows32 = Y.f32 ? cap : 1;
     const int maxF = Y.maxF > 0 ? Y.maxF : 1;
+    const size_t slots = Y.maxTop > 0 ? (size_t)Y.maxTop : 1; // feed-forward rows per token (a mixture of experts: one per chosen expert)
     if ((rc = dalloc(p, &Y.X, cap * E * 4))) return rc;
     if (Y.has_loop && (rc = dalloc(p, &Y.X0, cap * E * 4))) return rc;
     if ((rc = dalloc(p, &Y.Y, cap * E * 4))) return rc;
     if ((rc = dalloc(p, &Y.PROJ, cap * Y.maxP * 4))) return rc;
     if ((rc = dalloc(p, &Y.A32, rows32 * E * 4))) return rc;
     if ((rc = dalloc(p, &Y.ATT32, rows32 * Y.maxO * 4))) return rc;
-    if ((rc = dalloc(p, &Y.H32, rows32 * maxF * 4))) return rc;
+    if ((rc = dalloc(p, &Y.H32, rows32 * slots * maxF * 4))) return rc;
     if (!Y.f32) {
         if ((rc = dalloc(p, &Y.A16, cap * E * 2))) return rc;
         if ((rc = dalloc(p, &Y.ATT16, cap * Y.maxO * 2))) return rc;
-        if ((rc = dalloc(p, &Y.H16, cap * maxF * 2))) return rc;
+        if ((rc = dalloc(p, &Y.H16, cap * slots * maxF * 2))) return rc;
+    }
+    if (par) {
+        if ((rc = dalloc(p, &Y.A2_32, rows32 * E * 4))) return rc;
+        if ((rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;
+        if ((rc = dalloc(p, &Y.LAT32, rows32 * Y.maxL * 4))) return rc;
+        if (!Y.f32) {
+            if ((rc = dalloc(p, &Y.A2_16, cap * E * 2))) return rc;
+            if ((rc = dalloc(p, &Y.QU16, cap * Y.maxQU * 2))) return rc;
+            if ((rc = dalloc(p, &Y.LAT16, cap * Y.maxL * 2))) return rc;
+        }
+        if (Y.maxTop > 0) {
+            Y.max_tiles = (int)((cap * slots + 63) / 64) + Y.maxExperts;
+            if ((rc = dalloc(p, &Y.YS, cap * slots * E * 4))) return rc;
+            if ((rc = dalloc(p, &Y.moe_ids, cap * slots * 4))) return rc;
+            if ((rc = dalloc(p, &Y.moe_wts, cap * slots * 4))) return rc;
+            if ((rc = dalloc(p, &Y.moe_perm, cap * slots * 4))) return rc;
+            if ((rc = dalloc(p, &Y.tile_group, (size_t)Y.max_tiles * 4))) return rc;
+            if ((rc = dalloc(p, &Y.tile_row0, (size_t)Y.max_tiles * 4))) return rc;
+            if ((rc = dalloc(p, &Y.tile_rows, (size_t)Y.max_tiles * 4))) return rc;
+            CK(cudaMemset(Y.moe_ids, 0, cap * slots * 4));
+            CK(cudaMemset(Y.moe_wts, 0, cap * slots * 4));
+        }
     }
     if ((rc = dalloc(p, &Y.LOG, (size_t)(Y.f32 ? Y.logit_rows : 256) * c.vocab_size * 4))) return rc;
     if ((rc = dalloc(p, &Y.tok, cap * 4))) return rc;
@@ -484,8 +581,8 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
     {
         const char *e = getenv("B200_LAYERED_SPLITS");
         if (e && atoi(e) >= 1) Y.max_splits = atoi(e) > 8 ? 8 : atoi(e);
-        int maxH = 1, maxdv = 1;
-        for (const LyLayer &L : Y.layers) { if (L.s.heads > maxH) maxH = L.s.heads; if (L.s.value_dim > maxdv) maxdv = L.s.value_dim; }
+        int maxH = 1, maxdv = Y.max_att_dv;
+        for (const LyLayer &L : Y.layers) if (L.s.heads > maxH) maxH = L.s.heads;
         if (Y.max_splits > 1) {
             if ((rc = dalloc(p, &Y.split.o, (size_t)maxH * Y.max_splits * maxdv * 4))) return rc;
             if ((rc = dalloc(p, &Y.split.ml, (size_t)maxH * Y.max_splits * 2 * 4))) return rc;
@@ -546,13 +643,22 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
         const int m = n_rows - r0 < Y.logit_rows ? n_rows - r0 : Y.logit_rows;
         memcpy(p->h_ids, rows + r0, (size_t)m * 4);
         CK(cudaMemcpyAsync(Y.rows, p->h_ids, (size_t)m * 4, cudaMemcpyHostToDevice, p->stream));
-        ly::NormArgs a{};
-        a.x = Y.X; a.w_pre = Y.final_norm; a.gather = Y.rows; a.eps = Y.c.norm_eps; a.E = E;
-        a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
-        if ((rc = launch_k(p, false, ly::k_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
+        if (Y.c.block == B200_BLOCK_PARALLEL) {
+            ly::BlockNormArgs a = ly_block_norm_args(Y);
+            a.w1 = Y.final_norm; a.b1 = Y.final_norm_b; a.gather = Y.rows;
+            a.out1_32 = Y.f32 ? Y.A32 : nullptr; a.out1_16 = Y.f32 ? nullptr : Y.A16;
+            if ((rc = launch_k(p, false, ly::k_block_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
+        } else {
+            ly::NormArgs a{};
+            a.x = Y.X; a.w_pre = Y.final_norm; a.gather = Y.rows; a.eps = Y.c.norm_eps; a.E = E;
+            a.out32 = Y.f32 ? Y.A32 : nullptr; a.out16 = Y.f32 ? nullptr : Y.A16;
+            if ((rc = launch_k(p, false, ly::k_norm_rows, dim3(m), dim3(LY_NORM_THREADS), (size_t)E * 4, a))) return rc;
+        }
         LyTc t_head;
         if (Y.tc_head) { t_head.a = &Y.m_a; t_head.b = &Y.m_head; t_head.c = &Y.m_log_c; }
         if ((rc = ly_project<ly::EPI_STORE>(p, false, m, Y.A32, Y.A16, Y.head, nullptr, V, E, Y.LOG, nullptr, V, 0, &t_head))) return rc;
+        if (Y.c.logit_softcap > 0.0f &&
+            (rc = launch_k(p, false, ly::k_softcap, dim3((unsigned)(((size_t)m * V + 255) / 256)), dim3(256), (size_t)0, Y.LOG, (long long)m * V, Y.c.logit_softcap))) return rc;
         CK(cudaMemcpyAsync(logits_out + (size_t)r0 * V, Y.LOG, (size_t)m * V * 4, cudaMemcpyDeviceToHost, p->stream));
         CK(cudaStreamSynchronize(p->stream));
     }
@@ -565,9 +671,9 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
 static int ly_kv_reset(b200_plan *p) {
     Layered &Y = *p->ly;
     for (LyRun &R : Y.runs) {
-        const LyLayer &L = Y.layers[R.layer];
-        CK(cudaMemsetAsync(R.kc, 0, (size_t)Y.ring * L.kd * 4, p->stream));
-        CK(cudaMemsetAsync(R.vc, 0, (size_t)Y.ring * L.vd * 4, p->stream));
+        if (!R.own) continue;
+        CK(cudaMemsetAsync(R.kc, 0, (size_t)Y.ring * R.kw * 4, p->stream));
+        if (R.vc) CK(cudaMemsetAsync(R.vc, 0, (size_t)Y.ring * R.vw * 4, p->stream));
     }
     CK(cudaStreamSynchronize(p->stream));
     return B200_OK;
@@ -583,9 +689,10 @@ static int ly_read_buffer(b200_plan *p, const char *name, int layer, void *dst, 
     else if (s == "logits") { src = p->logits; sz = (size_t)Y.c.vocab_size * 4; }
     else if (s == "key_cache" || s == "value_cache") {
         if (layer < 0 || layer >= (int)Y.runs.size()) return fail(p, B200_ERR_BAD_ARG, "run out of range");
-        const LyLayer &L = Y.layers[Y.runs[layer].layer];
+        // latent attention keeps ONE cache per layer: "key_cache" = [latent | rotated shared key part] rows, no "value_cache"
         src = s == "key_cache" ? Y.runs[layer].kc : Y.runs[layer].vc;
-        sz = (size_t)Y.ring * (s == "key_cache" ? L.kd : L.vd) * 4;
+        sz = (size_t)Y.ring * (s == "key_cache" ? Y.runs[layer].kw : Y.runs[layer].vw) * 4;
+        if (!src) return fail(p, B200_ERR_BAD_ARG, "run %d has no %s", layer, name);
     } else return fail(p, B200_ERR_BAD_ARG, "unknown buffer %s", name);
     if (bytes < sz) sz = bytes;
     CK(cudaSetDevice(p->device));

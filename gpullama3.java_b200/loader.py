@@ -22,6 +22,7 @@ ARCH_LLAMA = 0
 ARCH_QWEN3 = 1
 ARCH_PHI3 = 2
 ARCH_PIBIDRA = 3
+ARCH_LATUSUN = 4
 
 GGML_BF16 = 30  # ggml's id for bfloat16; layered plans take their safetensors tensors under it
 _SAFETENSORS_TYPES = {"BF16": GGML_BF16, "F16": GGMLType.F16, "F32": GGMLType.F32}
@@ -53,7 +54,8 @@ class Configuration:
 
 @dataclass
 class LayerSpec:
-    """One layer of a layered model (``b200_layer_spec``): a windowed attention mixer and an optional gated feed-forward."""
+    """One layer of a layered model (``b200_layer_spec``): a mixer (windowed attention with its own key/value rows, or latent
+    attention over a cached low-rank latent) and an optional feed-forward (dense gated, or a mixture of experts)."""
     heads: int
     kv_heads: int
     key_dim: int
@@ -70,6 +72,17 @@ class LayerSpec:
     ff_dim: int = 0     # 0: no feed-forward
     ff_act: str = "gelu_tanh"
     mixer: str = "window_attention"
+    ff_kind: str = "dense"      # "dense" | "moe" (ff_dim = width of one expert)
+    ff_experts: int = 0
+    ff_top: int = 0
+    # latent attention: key_dim = unrotated query/key size per head, rot_dim = rotated size (= size of the shared key part)
+    rot_dim: int = 0
+    kv_rank: int = 0
+    kv_from: int = -1           # >= 0: reads that layer's cache and has no down-projection of its own
+    rope_dims: int = 0          # leading entries of the rotated part that turn
+    rope_layout: str = "half"   # "half": pair (i, i + dims/2) | "interleaved": pair (2i, 2i + 1)
+    rope_base: float = 10000.0
+    yarn: tuple = (0.0, 0.0, 0.0, 0.0)  # (factor, original length, fast, slow); factor 0: plain frequencies
 
 
 @dataclass
@@ -84,6 +97,9 @@ class LayeredConfiguration:
     layers: list = field(default_factory=list)
     loop: tuple | None = None  # (start, stop, times): layers [start, stop) run `times` passes over the same weights
     quantization: str = "BF16"
+    block: str = "sandwich"    # "sandwich": x += N(mixer(N x)); x += N(ff(N x)) | "parallel": x += mult * (mixer(LN1 x) + ff(LN2 x))
+    residual_mult: float = 1.0
+    logit_softcap: float = 0.0
 
     @property
     def n_layers(self):
@@ -175,8 +191,42 @@ def pibidra_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -
         layers, (int(loop["start"]), int(loop["stop"]), int(loop["times"])) if loop else None)
 
 
+# Latusun: mixer type -> (pairing of the rotation, output gate)
+LATUSUN_MIXERS = {"latent_attention": ("half", True), "latent_attention_2": ("interleaved", False)}
+
+
+def latusun_configuration(cfg: dict, tensor_shapes: dict, context_length: int) -> LayeredConfiguration:
+    """config.json of a Latusun model -> LayeredConfiguration: parallel blocks of latent attention and a sigmoid-routed mixture of
+    SiLU experts.  Every size and every constant that can differ between models comes from the file."""
+    layers = []
+    for i, lc in enumerate(cfg["layers"]):
+        if lc["type"] not in LATUSUN_MIXERS:
+            raise UnsupportedModel(f"layer {i}: mixer type {lc['type']!r} (Latusun layers are {sorted(LATUSUN_MIXERS)})")
+        layout, gate = LATUSUN_MIXERS[lc["type"]]
+        m, mlp = lc["mixer"], lc.get("mlp")
+        if mlp is not None and mlp.get("kind") != "moe":
+            raise UnsupportedModel(f"layer {i}: feed-forward kind {mlp.get('kind')!r}")
+        rot = m["rot"]
+        sc = rot.get("scaling")
+        kv_from = m.get("kv_from")
+        if f"l{i}.mix.dkv" in tensor_shapes and kv_from is not None:
+            raise UnsupportedModel(f"layer {i}: reads layer {kv_from}'s cache but carries a down-projection of its own")
+        layers.append(LayerSpec(
+            heads=int(m["heads"]), kv_heads=1, key_dim=int(m["dim"]), value_dim=int(m["vdim"]), window=int(context_length), bias_rows=0, bias_far=0.0,
+            score_scale=float(m["scale"]), softcap=0.0, sink=False, gate=gate, qkv_bias=False, qk_norm=False,
+            ff_dim=int(mlp["expert"]["ff"]) if mlp is not None else 0, ff_act="silu", mixer="latent_attention",
+            ff_kind="moe" if mlp is not None else "dense", ff_experts=int(mlp["router"]["experts"]) if mlp is not None else 0,
+            ff_top=int(mlp["router"]["top"]) if mlp is not None else 0,
+            rot_dim=int(m["rot_dim"]), kv_rank=int(m["kv_rank"]), kv_from=-1 if kv_from is None else int(kv_from),
+            rope_dims=int(rot["dims"]), rope_layout=layout, rope_base=float(rot["base"]),
+            yarn=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else (0.0, 0.0, 0.0, 0.0)))
+    return LayeredConfiguration(
+        ARCH_LATUSUN, int(cfg["width"]), int(cfg["vocab"]), int(context_length), float(cfg["norm"]["eps"]), 1.0, layers, None,
+        block="parallel", residual_mult=float(cfg.get("residual_mult", 1.0)), logit_softcap=float(cfg.get("logit_softcap") or 0.0))
+
+
 # config.json "architecture" -> (model type, configuration builder): the registry of safetensors model directories
-CONFIG_ARCHITECTURES = {"Pibidra": ("PIBIDRA", pibidra_configuration)}
+CONFIG_ARCHITECTURES = {"Pibidra": ("PIBIDRA", pibidra_configuration), "Latusun": ("LATUSUN", latusun_configuration)}
 DEFAULT_LAYERED_CONTEXT = 4096
 
 

@@ -37,17 +37,25 @@ class Config(C.Structure):
 class LayerSpec(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("mixer", "heads", "kv_heads", "key_dim", "value_dim", "window", "bias_rows")] + \
                [(n, C.c_float) for n in ("bias_far", "score_scale", "softcap")] + \
-               [(n, C.c_int32) for n in ("sink", "gate", "qkv_bias", "qk_norm", "ff_kind", "ff_dim", "ff_act")]
+               [(n, C.c_int32) for n in ("sink", "gate", "qkv_bias", "qk_norm", "ff_kind", "ff_dim", "ff_act")] + \
+               [(n, C.c_int32) for n in ("rot_dim", "kv_rank", "kv_from", "rope_dims", "rope_layout")] + \
+               [(n, C.c_float) for n in ("rope_base", "yarn_factor", "yarn_original", "yarn_fast", "yarn_slow")] + \
+               [(n, C.c_int32) for n in ("ff_experts", "ff_top")]
 
 
 class LayeredConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("arch", "width", "vocab_size", "n_layers", "context_length")] + \
                [("norm_eps", C.c_float), ("embedding_scale", C.c_float)] + \
-               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times", "compute")]
+               [(n, C.c_int32) for n in ("loop_start", "loop_stop", "loop_times", "compute", "block")] + \
+               [("residual_mult", C.c_float), ("logit_softcap", C.c_float)]
 
 
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
 ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+MIXERS = {"window_attention": 1, "latent_attention": 2}
+FF_KINDS = {"none": 0, "dense": 1, "moe": 2}
+ROPE_LAYOUTS = {"half": 0, "interleaved": 1}
+BLOCKS = {"sandwich": 0, "parallel": 1}
 
 
 class Tensor(C.Structure):

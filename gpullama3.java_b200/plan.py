@@ -65,16 +65,22 @@ def make_layered_config(model: Model, compute: str = "bfloat16"):
     cfg.norm_eps, cfg.embedding_scale = c.norm_eps, c.embedding_scale
     cfg.loop_start, cfg.loop_stop, cfg.loop_times = c.loop if c.loop is not None else (0, 0, -1)
     cfg.compute = {"bfloat16": native.COMPUTE_BF16, "bf16": native.COMPUTE_BF16, "float32": native.COMPUTE_F32, "f32": native.COMPUTE_F32}[compute]
+    cfg.block, cfg.residual_mult, cfg.logit_softcap = native.BLOCKS[c.block], c.residual_mult, c.logit_softcap
     specs = []
     for s in c.layers:
-        if s.mixer != "window_attention":
+        if s.mixer not in native.MIXERS:
             raise native.UnsupportedOperation(-2, f"mixer {s.mixer!r}")
         sp = native.LayerSpec()
-        sp.mixer = 1
+        sp.mixer = native.MIXERS[s.mixer]
         sp.heads, sp.kv_heads, sp.key_dim, sp.value_dim, sp.window = s.heads, s.kv_heads, s.key_dim, s.value_dim, s.window
         sp.bias_rows, sp.bias_far, sp.score_scale, sp.softcap = s.bias_rows, s.bias_far, s.score_scale, s.softcap
         sp.sink, sp.gate, sp.qkv_bias, sp.qk_norm = int(s.sink), int(s.gate), int(s.qkv_bias), int(s.qk_norm)
-        sp.ff_kind, sp.ff_dim, sp.ff_act = (1 if s.ff_dim > 0 else 0), s.ff_dim, native.ACTIVATIONS[s.ff_act]
+        ff_kind = s.ff_kind if s.ff_dim > 0 else "none"
+        sp.ff_kind, sp.ff_dim, sp.ff_act = native.FF_KINDS[ff_kind], s.ff_dim, native.ACTIVATIONS[s.ff_act]
+        sp.ff_experts, sp.ff_top = s.ff_experts, s.ff_top
+        sp.rot_dim, sp.kv_rank, sp.kv_from = s.rot_dim, s.kv_rank, s.kv_from
+        sp.rope_dims, sp.rope_layout, sp.rope_base = s.rope_dims, native.ROPE_LAYOUTS[s.rope_layout], s.rope_base
+        sp.yarn_factor, sp.yarn_original, sp.yarn_fast, sp.yarn_slow = s.yarn
         specs.append(sp)
     return cfg, specs
 

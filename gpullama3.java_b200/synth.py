@@ -468,3 +468,75 @@ def pibidra_model(cfg: dict, weights: dict, context_length: int):
     tensors = {k: (loader.GGML_BF16, tuple(reversed(v.shape)), bf16_bits(v).view(np.uint8).reshape(-1)) for k, v in weights.items()}
     config = loader.pibidra_configuration(cfg, {k: v.shape for k, v in weights.items()}, context_length)
     return loader.Model(None, config, "PIBIDRA", tensors)
+
+
+# ---- Latusun: seeded synthetic model directories --------------------------------------------------------------------------
+def latusun_layer(kind: str, heads: int, key_dim: int, rot_dim: int, value_dim: int, kv_rank: int, *, experts: int | None = 4, top: int = 1, ff: int = 32,
+                  scale: float | None = None, base: float = 10000.0, rope_dims: int | None = None, scaling: dict | None = None, kv_from: int | None = None) -> dict:
+    """One entry of config.json's "layers".  kind: "latent_attention" (half-split rotation, optional frequency blending, output gate) or
+    "latent_attention_2" (interleaved rotation, no gate, may read another layer's cache); experts = None: no feed-forward."""
+    rot = {"base": float(base), "dims": int(rot_dim if rope_dims is None else rope_dims)}
+    if scaling is not None:
+        rot["scaling"] = dict(scaling)
+    mixer = {"heads": heads, "dim": key_dim, "rot_dim": rot_dim, "vdim": value_dim, "kv_rank": kv_rank, "rot": rot,
+             "scale": float((key_dim + rot_dim) ** -0.5 if scale is None else scale)}
+    if kv_from is not None:
+        mixer["kv_from"] = int(kv_from)
+    mlp = None if experts is None else {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    return {"type": kind, "mixer": mixer, "mlp": mlp}
+
+
+def latusun_config(width: int, vocab: int, layers: list, eps: float = 1e-6, residual_mult: float = 0.5, logit_softcap: float | None = 20.0) -> dict:
+    cfg = {"architecture": "Latusun", "width": width, "vocab": vocab, "norm": {"eps": float(eps)}, "residual_mult": float(residual_mult), "layers": layers}
+    if logit_softcap is not None:
+        cfg["logit_softcap"] = float(logit_softcap)
+    return cfg
+
+
+def latusun_weights(cfg: dict, seed: int = 0) -> dict:
+    """name -> float32 array (linear weights [out][in]); values are BF16-representable."""
+    from .safetensors import bf16_bits, bf16_to_f32
+
+    rng = np.random.default_rng(seed)
+    E, V = cfg["width"], cfg["vocab"]
+    w = {}
+
+    def mat(o, i, gain=1.0):
+        return (rng.standard_normal((o, i)) * gain / np.sqrt(i)).astype(np.float32)
+
+    def norm(prefix):
+        w[prefix] = (1.0 + 0.2 * rng.standard_normal(E)).astype(np.float32)
+        w[prefix + ".b"] = (0.1 * rng.standard_normal(E)).astype(np.float32)
+
+    w["embed"] = rng.standard_normal((V, E)).astype(np.float32)
+    w["head"] = mat(V, E, 3.0)
+    norm("final.norm")
+    for i, lc in enumerate(cfg["layers"]):
+        m, p = lc["mixer"], f"l{i}."
+        H, dk, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        norm(p + "norm1")
+        w[p + "mix.q"] = mat(H * (dk + dr), E, 2.0)
+        if m.get("kv_from") is None:
+            w[p + "mix.dkv"] = mat(R + dr, E, 2.0)
+            w[p + "mix.dkv.norm"] = (1.0 + 0.3 * rng.standard_normal(R)).astype(np.float32)
+        w[p + "mix.uk"], w[p + "mix.uv"] = mat(H * dk, R, 2.0), mat(H * dv, R)
+        if lc["type"] == "latent_attention":
+            w[p + "mix.g"] = mat(H * dv, E, 2.0)
+        w[p + "mix.o"] = mat(E, H * dv)
+        if lc["mlp"] is not None:
+            norm(p + "norm2")
+            F, X = lc["mlp"]["expert"]["ff"], lc["mlp"]["router"]["experts"]
+            w[p + "mlp.router"] = mat(X, E, 2.0)
+            for e in range(X):
+                w[f"{p}mlp.e{e}.gate"], w[f"{p}mlp.e{e}.up"], w[f"{p}mlp.e{e}.down"] = mat(F, E, 2.0), mat(F, E), mat(E, F, 2.0)
+    return {k: bf16_to_f32(bf16_bits(v)).reshape(v.shape) for k, v in w.items()}
+
+
+def latusun_model(cfg: dict, weights: dict, context_length: int):
+    """In-memory loader.Model (benchmarks and tests: synthetic weights never touch the disk)."""
+    from . import loader
+    from .safetensors import bf16_bits
+
+    tensors = {k: (loader.GGML_BF16, tuple(reversed(v.shape)), bf16_bits(v).view(np.uint8).reshape(-1)) for k, v in weights.items()}
+    config = loader.latusun_configuration(cfg, {k: v.shape for k, v in weights.items()}, context_length)
+    return loader.Model(None, config, "LATUSUN", tensors)

@@ -44,6 +44,12 @@ extern "C" {
                              * logit cap and a learned bucketed distance bias, whole-projection q/k norm, sigmoid output gate, sandwich
                              * norms, a gated GELU feed-forward and a block of layers that is run several times over the same weights */
 
+#define B200_ARCH_LATUSUN 4 /* a layered design: every layer adds m * (mixer(LN1 x) + moe(LN2 x)) to the residual (both branches read the
+                             * same x; layer norms with weight and bias), the mixer is latent attention (a low-rank key/value latent and one
+                             * rotated key part shared by all heads are all that is cached; a layer may read another layer's cache), the
+                             * feed-forward a sigmoid-routed mixture of gated SiLU experts whose routing weight scales the expert's input,
+                             * and the logits end in a tanh cap */
+
 /* GGML tensor type ids accepted for weights (tensor/GGMLType.java:5-20) */
 #define B200_GGML_F32 0
 #define B200_GGML_F16 1
@@ -105,8 +111,19 @@ int b200_plan_create(const b200_config *cfg, const b200_tensor *tensors, int32_t
  * _batch_prefill, b200_decode_sequence, b200_kv_reset, b200_read_buffer) plus b200_forward_batch_logits.  Nothing of this
  * exists in the reference. */
 #define B200_MIXER_WINDOW_ATTENTION 1
+#define B200_MIXER_LATENT_ATTENTION 2 /* q = Wq a per head [key_dim unrotated | rot_dim rotated]; Wdkv a = [latent' (kv_rank) | shared key part
+                                       * (rot_dim)]; latent = RMS norm(latent') * w ("<layer>.mix.dkv.norm"); per head k = Wuk latent, v = Wuv
+                                       * latent; score = score_scale * (<q_u, k> + <rot q_r, rot shared>); causal softmax; optional sigmoid
+                                       * gate; Wo.  The cache holds [latent | rotated shared key part] per position; the kernels fold Wuk into
+                                       * the query and Wuv into the output, so keys and values are never expanded */
 #define B200_FF_NONE 0
 #define B200_FF_DENSE_GATED 1 /* down(act(gate x) * (up x)) */
+#define B200_FF_MOE 2         /* sum over the ff_top experts with the largest router scores of expert_e(s_e * x), expert = FF_DENSE_GATED without
+                               * biases ("<layer>.mlp.e<k>.{gate,up,down}"), s = sigmoid(Wrouter x) in FP32, not renormalised */
+#define B200_ROPE_HALF 0        /* pair (i, i + rot_dims / 2) */
+#define B200_ROPE_INTERLEAVED 1 /* pair (2i, 2i + 1) */
+#define B200_BLOCK_SANDWICH 0 /* x += N(mixer(N x)); x += N(ff(N x)) with (1 + w)-weighted RMS norms (Pibidra) */
+#define B200_BLOCK_PARALLEL 1 /* x += residual_mult * (mixer(LN1 x) + ff(LN2 x)), layer norms with weight and bias ("<layer>.norm1", ".norm1.b", ...) */
 #define B200_ACT_GELU_TANH 0
 #define B200_ACT_SILU 1
 #define B200_COMPUTE_BF16 0 /* prefill GEMM operands rounded to BF16, FP32 accumulation; decode FP32 activations x BF16 weights */
@@ -131,10 +148,22 @@ typedef struct b200_layer_spec {
     int32_t ff_kind;    /* B200_FF_* */
     int32_t ff_dim;
     int32_t ff_act;     /* B200_ACT_* */
+    /* B200_MIXER_LATENT_ATTENTION (key_dim = unrotated query/key size per head, value_dim = value size per head, kv_heads = 1, window = context) */
+    int32_t rot_dim;    /* rotated query/key size per head = size of the shared key part */
+    int32_t kv_rank;    /* latent size */
+    int32_t kv_from;    /* >= 0: no Wdkv of its own, reads the cache of that (earlier) layer; -1: its own */
+    int32_t rope_dims;  /* the first rope_dims entries of the rotated part turn, the rest pass unchanged (even, <= rot_dim) */
+    int32_t rope_layout; /* B200_ROPE_* */
+    float rope_base;    /* f_i = rope_base^(-2i / rope_dims) */
+    float yarn_factor;  /* > 0: f_i <- f_i / factor * ramp_i + f_i * (1 - ramp_i), cos and sin times 0.1 ln(factor) + 1; 0: plain */
+    float yarn_original, yarn_fast, yarn_slow; /* ramp from pair floor(d(fast)) to ceil(d(slow)), d(t) = rope_dims ln(original / (2 pi t)) / (2 ln base) */
+    /* B200_FF_MOE (ff_dim = width of one expert) */
+    int32_t ff_experts;
+    int32_t ff_top;
 } b200_layer_spec;
 
 typedef struct b200_layered_config {
-    int32_t arch;           /* B200_ARCH_PIBIDRA */
+    int32_t arch;           /* B200_ARCH_PIBIDRA, B200_ARCH_LATUSUN */
     int32_t width;
     int32_t vocab_size;
     int32_t n_layers;
@@ -143,6 +172,9 @@ typedef struct b200_layered_config {
     float embedding_scale;
     int32_t loop_start, loop_stop, loop_times; /* layers [loop_start, loop_stop) run loop_times passes; loop_times < 0: no loop */
     int32_t compute;        /* B200_COMPUTE_* */
+    int32_t block;          /* B200_BLOCK_* */
+    float residual_mult;    /* B200_BLOCK_PARALLEL: multiplies what a layer adds to the residual */
+    float logit_softcap;    /* > 0: logits <- cap * tanh(logits / cap) */
 } b200_layered_config;
 
 /* prefill_batch_size = the most tokens one b200_forward_batch_prefill / _batch_logits call takes (>= 1). */
