@@ -540,3 +540,6 @@ def latusun_model(cfg: dict, weights: dict, context_length: int):
     tensors = {k: (loader.GGML_BF16, tuple(reversed(v.shape)), bf16_bits(v).view(np.uint8).reshape(-1)) for k, v in weights.items()}
     config = loader.latusun_configuration(cfg, {k: v.shape for k, v in weights.items()}, context_length)
     return loader.Model(None, config, "LATUSUN", tensors)
+
+
+write_model_dir = write_pibidra_dir  # config.json + model.safetensors of any layered design

@@ -119,10 +119,16 @@ def latent_attention_mixer(a, W, pre, m, eps, *, interleaved, gated, cached):
     return o @ W[pre + "o"].T
 
 
-def moe_route(a, W, pre, top):
-    """(chosen experts [T, top], their weights [T, top]): sigmoid scores, the `top` largest, not renormalised."""
-    s = sigmoid(a @ W[pre + "router"].T)
-    idx = np.argsort(-s, axis=-1, kind="stable")[:, :top]
+def moe_route(a, W, pre, top, margins=None):
+    """(chosen experts [T, top], their weights [T, top]): sigmoid scores, the `top` largest, not renormalised.
+    margins (a list) receives, per token, the gap between the last chosen and the first rejected router logit."""
+    z = a @ W[pre + "router"].T
+    s = sigmoid(z)
+    order = np.argsort(-s, axis=-1, kind="stable")
+    idx = order[:, :top]
+    if margins is not None and top < z.shape[1]:
+        zs = np.take_along_axis(z, order, axis=-1)
+        margins.extend((zs[:, top - 1] - zs[:, top]).tolist())
     return idx, np.take_along_axis(s, idx, axis=-1)
 
 
@@ -130,10 +136,10 @@ def expert(h, W, pre):
     return (silu(h @ W[pre + "gate"].T) * (h @ W[pre + "up"].T)) @ W[pre + "down"].T
 
 
-def moe(a, W, pre, mlp):
+def moe(a, W, pre, mlp, margins=None):
     """sum over the chosen experts of expert(weight * input): the weight scales what the expert reads."""
     top = int(mlp["router"]["top"])
-    idx, wt = moe_route(a, W, pre, top)
+    idx, wt = moe_route(a, W, pre, top, margins)
     out = np.zeros((a.shape[0], W[pre + "e0.down"].shape[0]))
     for t in range(a.shape[0]):
         for k in range(top):
@@ -144,8 +150,8 @@ def moe(a, W, pre, mlp):
 MIXERS = {"latent_attention": dict(interleaved=False, gated=True), "latent_attention_2": dict(interleaved=True, gated=False)}
 
 
-def forward(cfg, W, tokens, want_layers: bool = False):
-    """Logits [T, vocab] (and the residual stream after every layer) of one whole sequence."""
+def forward(cfg, W, tokens, want_layers: bool = False, margins=None):
+    """Logits [T, vocab] (and the residual stream after every layer) of one whole sequence; margins: see moe_route."""
     eps = float(cfg["norm"]["eps"])
     mult = float(cfg.get("residual_mult", 1.0))
     x = W["embed"][np.asarray(tokens)].astype(np.float64)
@@ -163,7 +169,7 @@ def forward(cfg, W, tokens, want_layers: bool = False):
         if lc.get("mlp") is not None:
             if lc["mlp"]["kind"] != "moe":
                 raise ValueError(lc["mlp"]["kind"])
-            y = y + moe(layer_norm(x, W[pre + "norm2"], W[pre + "norm2.b"], eps), W, pre + "mlp.", lc["mlp"])
+            y = y + moe(layer_norm(x, W[pre + "norm2"], W[pre + "norm2.b"], eps), W, pre + "mlp.", lc["mlp"], margins)
         x = x + mult * y
         trace.append(x.copy())
     logits = layer_norm(x, W["final.norm"], W["final.norm.b"], eps) @ W["head"].T
