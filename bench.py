@@ -177,6 +177,92 @@ def compare_layered(pkg, lb, local: int, steps: int, warmup: int, sizes):
             "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
 
 
+# ---- --compare latusun: the parallel-block design beside the closest existing model (the Pibidra layered plan) at equal size -----
+# Both are layered plans with BF16 weights and the same projection kernels.  Equal size = same width, heads, vocabulary and
+# layer count; the Pibidra layers get the latent design's per-head query/key size (unrotated + rotated) and value size, one
+# key/value head per four query heads, and a dense feed-forward as wide as the experts one token uses (top x expert width).
+LATUSUN_SIZES = {
+    # name: (width, heads, unrotated, rotated, value, latent, experts, top, expert ff, vocab, layers)
+    # (unrotated + rotated = value = 64 / 128, so the closest model runs its tensor-core attention)
+    "small": (1024, 8, 48, 16, 64, 256, 8, 2, 1024, 32768, 4),
+    "lite-like": (2048, 16, 96, 32, 128, 512, 16, 4, 1408, 32768, 4),
+}
+
+
+def _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, dbytes, flop, kernel_names):
+    plan.decode_sequence(toks[:depth + warmup], depth + warmup, 0)
+    _, ms = plan.decode_sequence(toks[depth + warmup:depth + warmup + steps], steps, depth + warmup)
+    pp = []
+    for r in range(3 + 3):
+        plan.forward_batch_prefill(toks[:n_pp], 0)
+        if r >= 3:
+            pp.append(plan.prefill_info()[2])
+    pp_ms = float(np.mean(pp))
+    kern = {}
+    for which, kn in kernel_names:
+        kms, kb = plan.time_kernel(which, 5)
+        kern[kn] = {"us": kms * 1e3, "GB/s": kb / kms / 1e6, "frac_hbm": kb / kms / 1e6 / hbm}
+    return {"decode_tok_s": steps / ms * 1e3, "decode_ms": ms / steps, "decode_frac_hbm": dbytes / (ms / steps * 1e-3) / 1e9 / hbm,
+            "launches_per_decode": plan.launches_per_decode, "prefill_tok_s": n_pp / pp_ms * 1e3, "prefill_ms": pp_ms,
+            "prefill_tflops": flop / pp_ms / 1e9, "prefill_frac_tensor": flop / pp_ms / 1e9 / burst, "prefill_launches": plan.prefill_info()[1],
+            "decode_kernels": kern}
+
+
+def compare_latusun(pkg, lb, local: int, steps: int, warmup: int, sizes):
+    hbm, hbm_src = peaks()
+    burst, sustained, t_src = tensor_peak()
+    S = pkg.synth
+    out = {}
+    for name in sizes:
+        E, H, dk, dr, dv, R, X, top, F, V, NL = LATUSUN_SIZES[name]
+        depth, n_pp = 64, 512
+        ctx = max(depth + steps + warmup + 8, n_pp + 8)
+        toks = np.asarray(lb.synthetic_tokens(V, ctx), dtype=np.int32)
+        A, B = "latent_attention", "latent_attention_2"
+        blend = {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}
+        layers = []
+        for i in range(NL):  # gated / plain / plain reading the previous layer's cache / gated ...
+            kind = (A, B, B, A)[i % 4]
+            layers.append(S.latusun_layer(kind, H, dk, dr, dv, R, experts=X, top=top, ff=F, scaling=blend if kind == A else None,
+                                          kv_from=i - 1 if i % 4 == 2 else None))
+        cfg = S.latusun_config(E, V, layers)
+        w = S.latusun_weights(cfg, 1234)
+        streamed = 0  # weight elements one decode step reads
+        mac = 0       # multiply-adds per prompt token outside the attention's score / value products
+        for lc in layers:
+            own = lc["mixer"].get("kv_from") is None
+            gate = lc["type"] == A
+            proj = H * (dk + dr) * E + (R + dr) * E * own + H * dv * E * gate
+            mixer = proj + H * dk * R + H * dv * R + E * H * dv
+            ff = X * E + top * 3 * F * E
+            streamed += mixer + ff
+            mac += mixer + ff
+        att_mac = sum(NL * H * (2 * R + dr) * (i + 1) for i in range(n_pp))  # folded form: scores over R + dr, values over R
+        plan = pkg.B200MasterPlan.initialize_plan(S.latusun_model(cfg, w, ctx), prefill_batch_size=n_pp, device=local, compute="bfloat16")
+        row = {"latusun_bfloat16": _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, 2 * (streamed + V * E), 2.0 * mac * n_pp + 2.0 * att_mac,
+                                                ((0, "expert_gate_up"), (1, "expert_down"), (2, "q_dkv_gate"), (3, "attn_out"), (4, "classifier")))}
+        plan.free()
+        del w
+        # the closest existing model at equal size
+        G = max(1, H // 4)
+        Wn = ctx
+        pcfg = S.pibidra_config(E, V, [S.pibidra_layer(H, G, dk + dr, dv, Wn, top * F, bias_max=float(Wn)) for _ in range(NL)])
+        pw = S.pibidra_weights(pcfg, 1234, bias_rows=32)
+        per = (H * (dk + dr) + G * (dk + dr) + G * dv + H * dv) * E + H * dv * E + 3 * top * F * E
+        patt = sum(NL * H * (dk + dr + dv) * (i + 1) for i in range(n_pp))
+        plan = pkg.B200MasterPlan.initialize_plan(S.pibidra_model(pcfg, pw, ctx), prefill_batch_size=n_pp, device=local, compute="bfloat16")
+        row["pibidra_bfloat16"] = _layered_leg(plan, toks, depth, warmup, steps, n_pp, hbm, burst, 2 * (NL * per + V * E), 2.0 * NL * per * n_pp + 2.0 * patt,
+                                               ((0, "gate_up"), (1, "down"), (2, "qkvg"), (3, "attn_out"), (4, "classifier")))
+        plan.free()
+        del pw
+        row["config"] = {"width": E, "heads": H, "unrotated": dk, "rotated": dr, "value": dv, "latent": R, "experts": X, "top": top, "expert_ff": F, "vocab": V,
+                         "layers": NL, "closest": f"Pibidra: {G} key/value heads of {dk + dr} / {dv}, dense feed-forward {top * F}, window = context",
+                         "decode": f"tg{steps} from depth {depth + warmup}", "prefill": f"pp{n_pp} in one chunk from depth 0"}
+        out[name] = row
+    return {"metric": "latusun_vs_closest_model", "unit": "tok/s", "data": "synthetic", "dtype": "bf16 weights, f32 accumulate",
+            "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src, "tensor_tflops": burst, "tensor_source": t_src}, "sizes": out}
+
+
 class ClockSampler:
     """nvidia-smi clocks/throttle reasons sampled DURING the timed region."""
     Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
@@ -292,10 +378,10 @@ def main():
     ap.add_argument("--depth", type=int, default=-1, help="LlamaBench -d: KV positions filled before the timed steps (default: the warm-up steps)")
     ap.add_argument("--workload", default=WORKLOAD, choices=["llama-3-8b", "llama-3-70b", "llama-3.2-1b", "qwen3-4b"],
                     help="shape of the synthetic model (default: the BASELINE headline, Llama-3-8B; 70B is BASELINE config 5, meant for --gpus 2/4/8)")
-    ap.add_argument("--compare", default=None, choices=["pibidra"],
-                    help="instead of the headline workload: decode and prefill throughput of the layered design beside the closest GGUF model "
-                         "(FP16 Qwen3 plan) at equal sizes, with per-kernel rooflines; one JSON line")
-    ap.add_argument("--compare-sizes", default="1b-like,8b-like")
+    ap.add_argument("--compare", default=None, choices=["pibidra", "latusun"],
+                    help="instead of the headline workload: decode and prefill throughput of a layered design beside its closest existing model "
+                         "at equal sizes (pibidra: the FP16 Qwen3 plan; latusun: the Pibidra plan), with per-kernel rooflines; one JSON line")
+    ap.add_argument("--compare-sizes", default=None, help="comma-separated size names (pibidra: 1b-like,8b-like; latusun: small,lite-like)")
     args = ap.parse_args()
     K, W = args.steps, max(args.warmup, 3)
     if args.compare:
@@ -306,7 +392,10 @@ def main():
         pkg = ge.import_package()
         sampler = ClockSampler(local)
         sampler.start()
-        line = compare_layered(pkg, pkg.llama_bench, local, min(K, 64), W, args.compare_sizes.split(","))
+        if args.compare == "latusun":
+            line = compare_latusun(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "small,lite-like").split(","))
+        else:
+            line = compare_layered(pkg, pkg.llama_bench, local, min(K, 64), W, (args.compare_sizes or "1b-like,8b-like").split(","))
         line["clocks"] = sampler.stop()
         print(json.dumps(line))
         return 0

@@ -6,7 +6,7 @@
 //   * k_latent_prep      latent attention: RMS norm of the key/value latent, rotation of the shared key part and of every
 //                        head's rotated query part (table-driven: half-split or interleaved pairs, any blend of frequencies),
 //                        cache write [latent | rotated shared key part];
-//   * k_moe_route        sigmoid router in FP32 and selection of the `top` largest scores per row;
+//   * k_moe_topk         sigmoid of the router logits (an FP32 projection) and selection of the `top` largest per row;
 //   * k_moe_group        slots sorted by expert into tiles of 64 for the grouped projection kernels (GemmView);
 //   * k_softcap          x <- cap * tanh(x / cap) over a logits buffer.
 // The latent attention itself runs through k_window_attention: with W_uk folded into the query (q' = W_uk^T q_u per head)
@@ -111,12 +111,14 @@ __device__ __forceinline__ void rope_pair_index(int i, int dims, int layout, int
 
 // cache [ring][rank + dr];  Q [n][heads * (rank + dr)]: this kernel fills the rotated tail of every head, the folded-key
 // product fills the first rank entries;  qu16 (nullable) [n][heads * dk]: BF16 copy of the unrotated query parts.
-__global__ void __launch_bounds__(256) k_latent_prep(const float *__restrict__ P, int ldp, LatentArgs a, float *__restrict__ cache, int ring,
+// The rotated query parts are also written back into the projection row (the expanded-key prefill reads [q_u | rot q_r] there).
+// cache16 (nullable): BF16 twin of the cache row.
+__global__ void __launch_bounds__(256) k_latent_prep(float *__restrict__ P, int ldp, LatentArgs a, float *__restrict__ cache, bf16 *__restrict__ cache16, int ring,
                                                      float *__restrict__ Q, bf16 *__restrict__ qu16, const StepState *__restrict__ st) {
     __shared__ float red[32];
     const int r = blockIdx.x, tid = threadIdx.x;
     const int pos = st->pos + r, half = a.rope_dims / 2, kw = a.rank + a.dr;
-    const float *p = P + (size_t)r * ldp;
+    float *p = P + (size_t)r * ldp;
     const float *cs = a.cs + (size_t)pos * half * 2;
     if (a.kv_off >= 0) {
         const float *c = p + a.kv_off, *kr = c + a.rank;
@@ -134,6 +136,11 @@ __global__ void __launch_bounds__(256) k_latent_prep(const float *__restrict__ P
             row[a.rank + v] = kr[v] * co + kr[u] * si;
         }
         for (int i = a.rope_dims + tid; i < a.dr; i += 256) row[a.rank + i] = kr[i];
+        if (cache16) {
+            __syncthreads();
+            bf16 *row16 = cache16 + (size_t)(pos % ring) * kw;
+            for (int i = tid; i < kw; i += 256) row16[i] = __float2bfloat16_rn(row[i]);
+        }
     }
     const int hw = a.dk + a.dr;
     float *q = Q + (size_t)r * a.heads * kw;
@@ -141,10 +148,11 @@ __global__ void __launch_bounds__(256) k_latent_prep(const float *__restrict__ P
         const int h = e / half, i = e % half;
         int u, v;
         rope_pair_index(i, a.rope_dims, a.rope_layout, u, v);
-        const float *qr = p + a.q_off + (size_t)h * hw + a.dk;
+        float *qr = p + a.q_off + (size_t)h * hw + a.dk;
         const float co = cs[2 * i], si = cs[2 * i + 1];
-        q[(size_t)h * kw + a.rank + u] = qr[u] * co - qr[v] * si;
-        q[(size_t)h * kw + a.rank + v] = qr[v] * co + qr[u] * si;
+        const float ru = qr[u] * co - qr[v] * si, rv = qr[v] * co + qr[u] * si;
+        q[(size_t)h * kw + a.rank + u] = qr[u] = ru;
+        q[(size_t)h * kw + a.rank + v] = qr[v] = rv;
     }
     const int rest = a.dr - a.rope_dims;
     for (int e = tid; e < a.heads * rest; e += 256) {
@@ -161,42 +169,28 @@ __global__ void __launch_bounds__(256) k_latent_prep(const float *__restrict__ P
 // ---------------------------------------------------------------------------------------------------------------------
 // Mixture of experts: router and grouping.
 // ---------------------------------------------------------------------------------------------------------------------
-// One CTA of four warps per row: scores s_e = sigmoid(<Wr[e], x>) in FP32 (x FP32 or BF16), then the `top` largest (the
-// lowest index wins a tie); ids / wts [n][top], in order of falling score.  Dynamic shared memory: (E + experts) floats.
-template <typename IN_T>
-__global__ void __launch_bounds__(128) k_moe_route(const IN_T *__restrict__ X, const bf16 *__restrict__ Wr, int E, int experts, int top,
-                                                   int *__restrict__ ids, float *__restrict__ wts) {
-    extern __shared__ __align__(16) float sm[];
-    float *xs = sm, *sc = sm + E;
-    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid; i < E; i += 128) xs[i] = (float)X[(size_t)r * E + i];
-    __syncthreads();
-    for (int e = warp; e < experts; e += 4) {
-        const bf16 *w = Wr + (size_t)e * E;
-        float acc = 0.0f;
-        for (int i = lane; i < E; i += 32) acc = fmaf(__bfloat162float(w[i]), xs[i], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) sc[e] = 1.0f / (1.0f + expf(-acc));
-    }
-    __syncthreads();
-    if (warp == 0) {
-        for (int k = 0; k < top; k++) {
-            float best = -1.0f;
-            int bi = experts;
-            for (int e = lane; e < experts; e += 32)
-                if (sc[e] > best) { best = sc[e]; bi = e; }
+// Router logits z [n][experts] come from the projection kernels (FP32 accumulation).  One warp per row: s_e = sigmoid(z_e), then
+// the `top` largest (the lowest index wins a tie); ids / wts [n][top], in order of falling score.
+__global__ void __launch_bounds__(128) k_moe_topk(const float *__restrict__ Z, int n, int experts, int top, int *__restrict__ ids, float *__restrict__ wts) {
+    const int lane = threadIdx.x & 31, r = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (r >= n) return;
+    const float *z = Z + (size_t)r * experts;
+    unsigned long long taken_lo = 0ull; // experts this lane has given away, by (e / 32): lanes own e = lane, lane + 32, ...
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int bi = experts;
+        for (int e = lane, i = 0; e < experts; e += 32, i++)
+            if (!((taken_lo >> (i & 63)) & 1ull) && z[e] > best) { best = z[e]; bi = e; }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-            }
-            if (lane == 0) {
-                ids[(size_t)r * top + k] = bi;
-                wts[(size_t)r * top + k] = best;
-                sc[bi] = -2.0f; // taken
-            }
-            __syncwarp();
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if ((bi & 31) == lane && bi < experts) taken_lo |= 1ull << ((bi >> 5) & 63);
+        if (lane == 0) {
+            ids[(size_t)r * top + k] = bi < experts ? bi : 0;
+            wts[(size_t)r * top + k] = 1.0f / (1.0f + expf(-best));
         }
     }
 }
@@ -233,6 +227,15 @@ __global__ void __launch_bounds__(1024) k_moe_group(const int *__restrict__ ids,
         const int e = ids[s];
         perm[offs[e] + atomicAdd(&cursor[e], 1)] = s;
     }
+}
+
+// Expanded keys of a prefill chunk: the rotated shared key part of cached row j (BF16 twin, [.][kw], entries rank ..) goes behind
+// every head's unrotated key in KX [rows][heads * (dk + dr)].
+__global__ void __launch_bounds__(256) k_latent_spread(const bf16 *__restrict__ cache16, int kw, int rank, int dr, int heads, int dk, bf16 *__restrict__ KX, int rows) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x, per = (long long)heads * dr;
+    if (i >= per * rows) return;
+    const int j = (int)(i / per), h = (int)(i % per) / dr, e = (int)(i % per) % dr;
+    KX[((size_t)j * heads + h) * (dk + dr) + dk + e] = cache16[(size_t)j * kw + rank + e];
 }
 
 __global__ void __launch_bounds__(256) k_softcap(float *__restrict__ x, long long n, float cap) {

@@ -8,6 +8,8 @@
 //   -> W_uk folded into the query, one product per head                    (batched matvec / GEMM over blockIdx.y / z)
 //   -> attention over the cached rows [latent | shared key part]            (k_window_attention, one key/value head for all query heads)
 //   -> W_uv per head on the attention's latent-space output, times the sigmoid gate
+//      (BF16 prefill of layers whose key size = value size = 64 / 128 instead: keys and values expanded per head for the chunk,
+//       tensor-core attention kernel with the gate in its epilogue)
 //   -> output projection
 //   -> router -> (prefill: slots grouped by expert) -> gated expert projection -> expert down projection, one result row per slot.
 // The next block norm (or the final one) adds both branches to the residual.
@@ -86,7 +88,9 @@ static int ly_latent_sizes(b200_plan *p, int l, LyLayer &L, int n_layers, const 
     L.q_off = 0;
     L.kv_off = s.kv_from >= 0 ? -1 : L.qd;
     L.g_off = s.gate ? L.qd + (s.kv_from >= 0 ? 0 : L.kw) : -1;
-    L.P = L.qd + (s.kv_from >= 0 ? 0 : L.kw) + (s.gate ? L.gd : 0);
+    L.Pn = L.qd + (s.kv_from >= 0 ? 0 : L.kw) + (s.gate ? L.gd : 0);
+    // zero rows up to whole 128-row tiles, so that the prefill takes the tcgen05 GEMM whatever the latent size; the decode step streams Pn rows
+    L.P = p->ly->c.width % 64 == 0 ? (L.Pn + 127) / 128 * 128 : L.Pn;
     return B200_OK;
 }
 
@@ -100,6 +104,7 @@ static int ly_latent_upload(b200_plan *p, int l, LyLayer &L, const b200_tensor *
     if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1", E, &L.norm1))) return rc;
     if ((rc = ly_vec_f32(p, tensors, nt, pre + "norm1.b", E, &L.ln1_b))) return rc;
     if ((rc = dalloc(p, &L.w_proj, (size_t)L.P * E * 2))) return rc;
+    if (L.P > L.Pn) CK(cudaMemset(L.w_proj + (size_t)L.Pn * E, 0, (size_t)(L.P - L.Pn) * E * 2));
     if ((rc = ly_mat(p, tensors, nt, mx + "q", L.qd, E, L.w_proj, 0))) return rc;
     if (s.kv_from < 0) {
         if ((rc = ly_mat(p, tensors, nt, mx + "dkv", L.kw, E, L.w_proj, L.kv_off))) return rc;
@@ -119,6 +124,10 @@ static int ly_latent_upload(b200_plan *p, int l, LyLayer &L, const b200_tensor *
             for (int d = 0; d < s.key_dim; d++)
                 for (int j = 0; j < s.kv_rank; j++)
                     tr[((size_t)h * s.kv_rank + j) * s.key_dim + d] = src[((size_t)h * s.key_dim + d) * s.kv_rank + j];
+        if (L.expand) {
+            if ((rc = dalloc(p, &L.w_uk, tr.size() * 2))) return rc;
+            if ((rc = ly_mat(p, tensors, nt, mx + "uk", s.heads * s.key_dim, s.kv_rank, L.w_uk, 0))) return rc;
+        }
         if ((rc = dalloc(p, &L.w_ukT, tr.size() * 2))) return rc;
         if (p->up.on) { if ((rc = up_h2d(p, L.w_ukT, tr.data(), tr.size() * 2))) return rc; }
         else { CK(cudaMemcpy(L.w_ukT, tr.data(), tr.size() * 2, cudaMemcpyHostToDevice)); p->up.h2d_bytes += (int64_t)tr.size() * 2; }
@@ -201,55 +210,80 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
             if (L.tc_proj) { t_proj.a = &Y.m_a; t_proj.b = &L.m_proj; t_proj.c = &Y.m_proj_c; }
             if (L.tc_o) { t_o.a = &L.m_att; t_o.b = &L.m_o; t_o.c = &Y.m_y_c; }
         }
-        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, nullptr, L.P, E, Y.PROJ, nullptr, Y.maxP, 0, &t_proj))) return rc;
+        if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A32, Y.A16, L.w_proj, nullptr, decode ? L.Pn : L.P, E, Y.PROJ, nullptr, Y.maxP, 0, &t_proj))) return rc;
         nl++;
         ly::LatentArgs la{};
         la.heads = s.heads; la.dk = s.key_dim; la.dr = s.rot_dim; la.rank = s.kv_rank; la.q_off = L.q_off; la.kv_off = L.kv_off;
         la.cnorm = L.cnorm; la.cs = L.rope; la.rope_dims = s.rope_dims; la.rope_layout = s.rope_layout; la.eps = Y.c.norm_eps;
-        if ((rc = launch_k(p, false, ly::k_latent_prep, dim3(n), dim3(256), (size_t)0, (const float *)Y.PROJ, Y.maxP, la, R.kc, Y.ring, Y.Q, h16 ? Y.QU16 : nullptr, st))) return rc;
+        if ((rc = launch_k(p, false, ly::k_latent_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, la, R.kc, R.own ? R.kc16 : (ly::bf16 *)nullptr, Y.ring, Y.Q, h16 ? Y.QU16 : nullptr, st))) return rc;
         nl++;
-        { // folded query: Q[h][0 .. rank) = W_uk[h]^T q_u[h]
+        if (h16 && L.expand && R.kc16) {
+            // BF16 prefill, key size = value size = 64 / 128: keys and values of every cached position up to the chunk's end are
+            // expanded per head (two GEMMs over the BF16 twin of the cache), the rotated shared part is copied behind each head's
+            // key, and the tensor-core attention kernel reads [q_u | rot q_r] from the projection rows; gate in its epilogue
+            const int DK = s.key_dim + s.rot_dim, M = Y.pf_pos + n;
             ly::GemmView gv{};
-            ly::MvView mv{};
-            mv.w_bs = gv.w_bs = (long long)s.kv_rank * s.key_dim;
-            mv.x_bs = s.key_dim + s.rot_dim; mv.y_bs = L.kw;
-            gv.lda = h16 ? s.heads * s.key_dim : Y.maxP; gv.a_bs = h16 ? s.key_dim : s.key_dim + s.rot_dim; gv.c_bs = L.kw;
-            if ((rc = ly_project_view<ly::EPI_STORE>(p, decode, n, Y.PROJ + L.q_off, Y.QU16, L.w_ukT, s.kv_rank, s.key_dim, Y.Q, nullptr, L.qw, 0, gv, mv, s.heads, s.heads, 0))) return rc;
+            gv.lda = L.kw; gv.w_bs = (long long)s.key_dim * s.kv_rank; gv.c_bs = DK;
+            if ((rc = ly_project_view<ly::EPI_STORE>(p, false, M, nullptr, R.kc16, L.w_uk, s.key_dim, s.kv_rank, nullptr, Y.KX16, s.heads * DK, 0, gv, ly::MvView{}, 1, s.heads, 0))) return rc;
+            ly::GemmView gv2{};
+            gv2.lda = L.kw;
+            if ((rc = ly_project_view<ly::EPI_STORE>(p, false, M, nullptr, R.kc16, L.w_uv, L.gd, s.kv_rank, nullptr, Y.VX16, L.gd, 0, gv2, ly::MvView{}, 1, 1, 0))) return rc;
+            const long long cells = (long long)M * s.heads * s.rot_dim;
+            if (cells > 0 && (rc = launch_k(p, false, ly::k_latent_spread, dim3((unsigned)((cells + 255) / 256)), dim3(256), (size_t)0, (const ly::bf16 *)R.kc16, L.kw, s.kv_rank, s.rot_dim,
+                                            s.heads, s.key_dim, Y.KX16, M))) return rc;
+            ly::WindowAttn wa{};
+            wa.heads = wa.kv_heads = s.heads; wa.dk = DK; wa.dv = s.value_dim; wa.window = s.window; wa.ring = Y.ring; wa.ldk = s.heads * DK; wa.ldv = L.gd;
+            wa.scale = s.score_scale; wa.gate = s.gate; wa.gate_off = L.g_off - L.q_off; wa.eps = Y.c.norm_eps;
+            const dim3 grid((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, s.heads);
+            if (DK == 64) rc = launch_k(p, false, ly::k_window_attention_mma<64, 64>, grid, dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<64, 64>(s.window), (const float *)(Y.PROJ + L.q_off),
+                                        Y.maxP, wa, (const ly::bf16 *)Y.KX16, (const ly::bf16 *)Y.VX16, st, n, Y.ATT16, L.gd);
+            else rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, grid, dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(s.window), (const float *)(Y.PROJ + L.q_off),
+                               Y.maxP, wa, (const ly::bf16 *)Y.KX16, (const ly::bf16 *)Y.VX16, st, n, Y.ATT16, L.gd);
+            if (rc) return rc;
+            nl += 4;
+        } else {
+            { // folded query: Q[h][0 .. rank) = W_uk[h]^T q_u[h]
+                ly::GemmView gv{};
+                ly::MvView mv{};
+                mv.w_bs = gv.w_bs = (long long)s.kv_rank * s.key_dim;
+                mv.x_bs = s.key_dim + s.rot_dim; mv.y_bs = L.kw;
+                gv.lda = h16 ? s.heads * s.key_dim : Y.maxP; gv.a_bs = h16 ? s.key_dim : s.key_dim + s.rot_dim; gv.c_bs = L.kw;
+                if ((rc = ly_project_view<ly::EPI_STORE>(p, decode, n, Y.PROJ + L.q_off, Y.QU16, L.w_ukT, s.kv_rank, s.key_dim, Y.Q, nullptr, L.qw, 0, gv, mv, s.heads, s.heads, 0))) return rc;
+                nl++;
+            }
+            ly::WindowAttn wa{};
+            wa.heads = s.heads; wa.kv_heads = 1; wa.dk = L.kw; wa.dv = s.kv_rank; wa.window = s.window; wa.ring = Y.ring; wa.ldk = wa.ldv = L.kw;
+            wa.scale = s.score_scale; wa.softcap = 0.0f; wa.eps = Y.c.norm_eps;
+            const size_t asm_ = ly_att_smem(wa.dk, wa.window);
+            if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.Q, L.qw, wa,
+                                   (const float *)R.kc, (const float *)R.kc, st, Y.LAT16, L.lw, ly::KeySplit{nullptr, nullptr, nullptr});
+            else {
+                int sp = 1;
+                if (decode && Y.split.o && s.window >= 64) { sp = p->n_sms / s.heads; if (sp > Y.max_splits) sp = Y.max_splits; if (sp < 1) sp = 1; }
+                rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, s.heads, sp), dim3(LY_ATT_THREADS), asm_, (const float *)Y.Q, L.qw, wa,
+                              (const float *)R.kc, (const float *)R.kc, st, Y.LAT32, L.lw, sp > 1 ? Y.split : ly::KeySplit{nullptr, nullptr, nullptr});
+            }
+            if (rc) return rc;
             nl++;
-        }
-        ly::WindowAttn wa{};
-        wa.heads = s.heads; wa.kv_heads = 1; wa.dk = L.kw; wa.dv = s.kv_rank; wa.window = s.window; wa.ring = Y.ring; wa.ldk = wa.ldv = L.kw;
-        wa.scale = s.score_scale; wa.softcap = 0.0f; wa.eps = Y.c.norm_eps;
-        const size_t asm_ = ly_att_smem(wa.dk, wa.window);
-        if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.Q, L.qw, wa,
-                               (const float *)R.kc, (const float *)R.kc, st, Y.LAT16, L.lw, ly::KeySplit{nullptr, nullptr, nullptr});
-        else {
-            int sp = 1;
-            if (decode && Y.split.o && s.window >= 64) { sp = p->n_sms / s.heads; if (sp > Y.max_splits) sp = Y.max_splits; if (sp < 1) sp = 1; }
-            rc = launch_k(p, false, ly::k_window_attention<float>, dim3(n, s.heads, sp), dim3(LY_ATT_THREADS), asm_, (const float *)Y.Q, L.qw, wa,
-                          (const float *)R.kc, (const float *)R.kc, st, Y.LAT32, L.lw, sp > 1 ? Y.split : ly::KeySplit{nullptr, nullptr, nullptr});
-        }
-        if (rc) return rc;
-        nl++;
-        { // per head: W_uv on the latent-space output, times sigmoid(gate)
-            ly::GemmView gv{};
-            ly::MvView mv{};
-            mv.w_bs = gv.w_bs = (long long)s.value_dim * s.kv_rank;
-            mv.x_bs = s.kv_rank; mv.y_bs = s.value_dim; mv.mul = s.gate ? Y.PROJ + L.g_off : nullptr;
-            gv.lda = L.lw; gv.a_bs = s.kv_rank; gv.c_bs = s.value_dim; gv.mul = mv.mul; gv.ldmul = Y.maxP;
-            if ((rc = ly_project_view<ly::EPI_STORE>(p, decode, n, Y.LAT32, Y.LAT16, L.w_uv, s.value_dim, s.kv_rank, Y.ATT32, h16 ? Y.ATT16 : nullptr, L.gd, 0, gv, mv,
-                                                     s.heads, s.heads, 0))) return rc;
-            nl++;
+            { // per head: W_uv on the latent-space output, times sigmoid(gate)
+                ly::GemmView gv{};
+                ly::MvView mv{};
+                mv.w_bs = gv.w_bs = (long long)s.value_dim * s.kv_rank;
+                mv.x_bs = s.kv_rank; mv.y_bs = s.value_dim; mv.mul = s.gate ? Y.PROJ + L.g_off : nullptr;
+                gv.lda = L.lw; gv.a_bs = s.kv_rank; gv.c_bs = s.value_dim; gv.mul = mv.mul; gv.ldmul = Y.maxP;
+                if ((rc = ly_project_view<ly::EPI_STORE>(p, decode, n, Y.LAT32, Y.LAT16, L.w_uv, s.value_dim, s.kv_rank, Y.ATT32, h16 ? Y.ATT16 : nullptr, L.gd, 0, gv, mv,
+                                                         s.heads, s.heads, 0))) return rc;
+                nl++;
+            }
         }
         if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.ATT32, Y.ATT16, L.w_o, nullptr, E, L.gd, Y.Y, nullptr, E, 0, &t_o))) return rc;
         nl++;
         pend_a = Y.Y;
         if (moe) {
             const int F = s.ff_dim, X = s.ff_experts, top = s.ff_top;
-            const size_t rsm = (size_t)(E + X) * 4;
-            if (h16) rc = launch_k(p, false, ly::k_moe_route<ly::bf16>, dim3(n), dim3(128), rsm, (const ly::bf16 *)Y.A2_16, (const ly::bf16 *)L.w_router, E, X, top, Y.moe_ids, Y.moe_wts);
-            else rc = launch_k(p, false, ly::k_moe_route<float>, dim3(n), dim3(128), rsm, (const float *)Y.A2_32, (const ly::bf16 *)L.w_router, E, X, top, Y.moe_ids, Y.moe_wts);
-            if (rc) return rc;
+            if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A2_32, Y.A2_16, L.w_router, nullptr, X, E, Y.ZR, nullptr, X, 0))) return rc;
+            nl++;
+            if ((rc = launch_k(p, false, ly::k_moe_topk, dim3((n + 3) / 4), dim3(128), (size_t)0, (const float *)Y.ZR, n, X, top, Y.moe_ids, Y.moe_wts))) return rc;
             nl++;
             int tiles = 0;
             if (!decode) {

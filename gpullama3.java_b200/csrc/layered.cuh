@@ -436,6 +436,7 @@ struct WindowAttn {
     const float *qnorm, *knorm;  // whole-projection RMS norm weights [heads*dk], [kv_heads*dk], used as stored (nullable: no norm)
     int sink;                    // 1: the softmax denominator carries one extra exp(0)
     int gate;                    // 1: the output is multiplied by sigmoid(g), g the fourth block of the fused projection
+    int gate_off;                // column of g in a projection row; < 0: behind q | k | v (heads*dk + kv_heads*dk + kv_heads*dv)
     float eps;
 };
 // Row layout of the fused projection output: [q: heads*dk | k: kv_heads*dk | v: kv_heads*dv | g: heads*dv]
@@ -580,7 +581,7 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
     const float inv = splits > 1 ? 1.0f : 1.0f / (sum + (a.sink ? expf(-mx) : 0.0f)); // split runs keep the unnormalised sum
     const size_t cell = (size_t)r * a.heads + h; // (row, head)
     float *my_o = splits > 1 ? ks_.o + (cell * splits + z) * a.dv : nullptr;
-    const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * a.dv;
+    const float *gate = P + (size_t)r * ldp + (a.gate_off >= 0 ? a.gate_off : qd + kd + vd) + (size_t)h * a.dv;
     const int vw = ((a.dv & 3) == 0 && (a.ldv & 3) == 0) ? 4 : 1; // value elements per thread
     int tpk = (a.dv + vw - 1) / vw;                             // threads per key
     if (tpk > LY_ATT_THREADS) tpk = LY_ATT_THREADS;
@@ -840,7 +841,7 @@ __global__ void __launch_bounds__(LY_ATT_MMA_THREADS) k_window_attention_mma(con
         if (!vrow[rr]) continue;
         const int r = r0 + warp * 16 + g + rr * 8;
         const float inv = lrow[rr] > 0.0f ? 1.0f / lrow[rr] : 0.0f;
-        const float *gate = P + (size_t)r * ldp + qd + kd + vd + (size_t)h * DV;
+        const float *gate = P + (size_t)r * ldp + (a.gate_off >= 0 ? a.gate_off : qd + kd + vd) + (size_t)h * DV;
 #pragma unroll
         for (int j = 0; j < DV / 8; j++) {
             const int d = j * 8 + 2 * t;

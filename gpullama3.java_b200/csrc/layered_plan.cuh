@@ -24,6 +24,7 @@
 struct LyLayer {
     b200_layer_spec s{};
     int qd = 0, kd = 0, vd = 0, gd = 0, P = 0; // fused projection: q | k | v | gate rows
+    int Pn = 0;                                // rows of the fused projection that carry weights (P may be padded with zero rows)
     ly::bf16 *w_proj = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_down = nullptr;
     float *b_proj = nullptr;
     float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr, *qnorm = nullptr, *knorm = nullptr, *rel = nullptr;
@@ -32,6 +33,8 @@ struct LyLayer {
     // kw = kv_rank + rot_dim; folded query row qw = heads * kw; attention output in latent space lw = heads * kv_rank
     int q_off = 0, kv_off = -1, g_off = -1, kw = 0, qw = 0, lw = 0;
     ly::bf16 *w_ukT = nullptr, *w_uv = nullptr; // [heads][kv_rank][key_dim] (W_uk transposed per head at upload), [heads][value_dim][kv_rank]
+    ly::bf16 *w_uk = nullptr;                   // [heads * key_dim][kv_rank] as stored: the BF16 prefill that expands keys per head reads it
+    bool expand = false;                        // BF16 prefill through expanded keys / values and the tensor-core attention kernel
     float *cnorm = nullptr;
     const float *rope = nullptr;                // [context][rope_dims / 2][2], shared between layers with the same rotation
     // parallel block: biases of the two layer norms; mixture of experts: router [experts][width], w_gu = [experts][2 ff][width],
@@ -73,8 +76,10 @@ struct Layered {
     CUtensorMap m_a, m_head, m_proj_c, m_y_c, m_log_c;
     // parallel block / latent attention / mixture of experts
     float *final_norm_b = nullptr;
-    float *A2_32 = nullptr, *Q = nullptr, *LAT32 = nullptr, *YS = nullptr, *moe_wts = nullptr;
+    float *A2_32 = nullptr, *Q = nullptr, *LAT32 = nullptr, *YS = nullptr, *moe_wts = nullptr, *ZR = nullptr;
     ly::bf16 *A2_16 = nullptr, *QU16 = nullptr, *LAT16 = nullptr;
+    ly::bf16 *KX16 = nullptr, *VX16 = nullptr; // keys / values of one layer expanded per head for a prefill chunk: [context][heads * size]
+    int maxKX = 0, maxVX = 0, pf_pos = 0;      // pf_pos: first position of the chunk being enqueued
     int *moe_ids = nullptr, *moe_perm = nullptr, *tile_group = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr;
     int maxQ = 0, maxL = 0, maxQU = 0, maxTop = 0, maxExperts = 0, max_tiles = 0, max_att_dv = 1;
     std::vector<std::pair<std::vector<float>, float *>> rope_tables; // (key, device table)
@@ -145,7 +150,7 @@ static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
     a.ldk = L.kd; a.ldv = L.vd;
     a.scale = L.s.score_scale; a.softcap = L.s.softcap;
     a.rel = L.rel; a.bucket = L.bucket; a.qnorm = L.qnorm; a.knorm = L.knorm;
-    a.sink = L.s.sink; a.gate = L.s.gate; a.eps = Y.c.norm_eps;
+    a.sink = L.s.sink; a.gate = L.s.gate; a.gate_off = -1; a.eps = Y.c.norm_eps;
     return a;
 }
 
@@ -367,7 +372,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if ((rc = ly_latent_sizes(p, l, L, c.n_layers, specs))) return rc;
             if (s.ff_kind != B200_FF_NONE && s.ff_kind != B200_FF_MOE) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: feed-forward kind %d in a parallel block", l, s.ff_kind);
             if (s.ff_kind == B200_FF_MOE) {
-                if (s.ff_dim <= 0 || s.ff_experts <= 0 || s.ff_top <= 0 || s.ff_top > s.ff_experts || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU))
+                if (s.ff_dim <= 0 || s.ff_experts <= 0 || s.ff_experts > 2048 || s.ff_top <= 0 || s.ff_top > s.ff_experts || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU))
                     return fail(p, B200_ERR_BAD_ARG, "layer %d: %d experts of width %d, %d chosen, activation %d", l, s.ff_experts, s.ff_dim, s.ff_top, s.ff_act);
                 if (s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
                 if (s.ff_top > Y.maxTop) Y.maxTop = s.ff_top;
@@ -391,7 +396,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (s.ff_kind == B200_FF_DENSE_GATED && (s.ff_dim <= 0 || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU)))
             return fail(p, B200_ERR_BAD_ARG, "layer %d: feed-forward width %d / activation %d", l, s.ff_dim, s.ff_act);
         L.qd = s.heads * s.key_dim; L.kd = s.kv_heads * s.key_dim; L.vd = s.kv_heads * s.value_dim; L.gd = s.heads * s.value_dim;
-        L.P = L.qd + L.kd + L.vd + (s.gate ? L.gd : 0);
+        L.P = L.Pn = L.qd + L.kd + L.vd + (s.gate ? L.gd : 0);
         if (L.P > Y.maxP) Y.maxP = L.P;
         if (L.gd > Y.maxO) Y.maxO = L.gd;
         if (s.ff_kind == B200_FF_DENSE_GATED && s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
@@ -409,8 +414,6 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (!attrs) {
             CK(set_max_dyn(ly::k_norm_rows, Y.smem_max));
             CK(set_max_dyn(ly::k_block_norm_rows, Y.smem_max));
-            CK(set_max_dyn(ly::k_moe_route<float>, Y.smem_max));
-            CK(set_max_dyn(ly::k_moe_route<ly::bf16>, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_STORE>, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_GATED>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention<float>, Y.smem_max));
@@ -420,6 +423,19 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             attrs = true;
         }
     }
+    // Latent attention, BF16 prefill: layers whose per-head key size (unrotated + rotated) equals their value size, 64 or 128, expand
+    // keys and values per head for the chunk and run the tensor-core attention kernel; all others attend in the folded form
+    if (par && !Y.f32 && Y.att_mma && Y.cap > 1 && Y.maxP % 4 == 0)
+        for (LyLayer &L : Y.layers) {
+            const int DK = L.s.key_dim + L.s.rot_dim;
+            const bool s64 = DK == 64 && L.s.value_dim == 64, s128 = DK == 128 && L.s.value_dim == 128;
+            const size_t need = s64 ? ly::att_mma_smem_bytes<64, 64>(L.s.window) : ly::att_mma_smem_bytes<128, 128>(L.s.window);
+            L.expand = (s64 || s128) && need <= (size_t)Y.smem_max && (!L.s.gate || L.g_off % 2 == 0) && L.s.key_dim % 8 == 0;
+            if (L.expand) {
+                if (L.s.heads * DK > Y.maxKX) Y.maxKX = L.s.heads * DK;
+                if (L.gd > Y.maxVX) Y.maxVX = L.gd;
+            }
+        }
     // ring: a step of `cap` rows must not overwrite keys its first rows still see; never more slots than positions
     {
         long long want = (long long)Y.max_window - 1 + Y.cap;
@@ -515,9 +531,13 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (L.s.mixer == B200_MIXER_LATENT_ATTENTION) {
             // one cache of [latent | rotated shared key part] rows; a layer that reads another layer's cache points at it (runs = layers here)
             R.kw = L.kw;
-            if (L.s.kv_from >= 0) { R.own = false; R.kc = Y.runs[L.s.kv_from].kc; continue; }
+            if (L.s.kv_from >= 0) { R.own = false; R.kc = Y.runs[L.s.kv_from].kc; R.kc16 = Y.runs[L.s.kv_from].kc16; continue; }
             if ((rc = dalloc(p, &R.kc, (size_t)Y.ring * L.kw * 4))) return rc;
             CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kw * 4));
+            if (Y.maxKX > 0) { // BF16 twin rows: the A operand of the per-chunk key / value expansion
+                if ((rc = dalloc(p, &R.kc16, (size_t)Y.ring * L.kw * 2))) return rc;
+                CK(cudaMemset(R.kc16, 0, (size_t)Y.ring * L.kw * 2));
+            }
             continue;
         }
         R.kw = L.kd; R.vw = L.vd;
@@ -554,6 +574,10 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if ((rc = dalloc(p, &Y.H16, cap * slots * maxF * 2))) return rc;
     }
     if (par) {
+        if (Y.maxKX > 0) {
+            if ((rc = dalloc(p, &Y.KX16, (size_t)Y.ring * Y.maxKX * 2))) return rc;
+            if ((rc = dalloc(p, &Y.VX16, (size_t)Y.ring * Y.maxVX * 2))) return rc;
+        }
         if ((rc = dalloc(p, &Y.A2_32, rows32 * E * 4))) return rc;
         if ((rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;
         if ((rc = dalloc(p, &Y.LAT32, rows32 * Y.maxL * 4))) return rc;
@@ -565,6 +589,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (Y.maxTop > 0) {
             Y.max_tiles = (int)((cap * slots + 63) / 64) + Y.maxExperts;
             if ((rc = dalloc(p, &Y.YS, cap * slots * E * 4))) return rc;
+            if ((rc = dalloc(p, &Y.ZR, cap * Y.maxExperts * 4))) return rc;
             if ((rc = dalloc(p, &Y.moe_ids, cap * slots * 4))) return rc;
             if ((rc = dalloc(p, &Y.moe_wts, cap * slots * 4))) return rc;
             if ((rc = dalloc(p, &Y.moe_perm, cap * slots * 4))) return rc;
@@ -635,6 +660,7 @@ static int ly_batch(b200_plan *p, const int32_t *tokens, int n, int start_pos, c
     h->token = tokens[0]; h->pos = start_pos;
     CK(cudaMemcpyAsync(Y.st_pf, h, sizeof(StepState), cudaMemcpyHostToDevice, p->stream));
     CK(cudaEventRecord(p->ev0, p->stream));
+    Y.pf_pos = start_pos;
     if ((rc = ly_enqueue(p, false, n, Y.st_pf, Y.tok, false, trace_out ? Y.trace : nullptr, &p->launches_prefill))) return rc;
     CK(cudaEventRecord(p->ev1, p->stream));
     CK(cudaStreamSynchronize(p->stream)); // h_ids / h_st are reused below
@@ -716,8 +742,8 @@ static int ly_time_kernel(b200_plan *p, int which, int reps, float *avg_ms, int6
                 return ly_project<ly::EPI_GATED>(p, true, 1, Y.A32, nullptr, L->w_gu, nullptr, L->s.ff_dim, E, Y.H32, nullptr, L->s.ff_dim, L->s.ff_act);
         case 1: if (!L->w_down) return B200_OK; bytes = (int64_t)L->s.ff_dim * E * 2; launches++;
                 return ly_project<ly::EPI_STORE>(p, true, 1, Y.H32, nullptr, L->w_down, nullptr, E, L->s.ff_dim, Y.Y, nullptr, E, 0);
-        case 2: bytes = (int64_t)L->P * E * 2; launches++;
-                return ly_project<ly::EPI_STORE>(p, true, 1, Y.A32, nullptr, L->w_proj, L->b_proj, L->P, E, Y.PROJ, nullptr, Y.maxP, 0);
+        case 2: bytes = (int64_t)L->Pn * E * 2; launches++;
+                return ly_project<ly::EPI_STORE>(p, true, 1, Y.A32, nullptr, L->w_proj, L->b_proj, L->Pn, E, Y.PROJ, nullptr, Y.maxP, 0);
         case 3: bytes = (int64_t)L->gd * E * 2; launches++;
                 return ly_project<ly::EPI_STORE>(p, true, 1, Y.ATT32, nullptr, L->w_o, nullptr, E, L->gd, Y.Y, nullptr, E, 0);
         default: bytes = (int64_t)Y.c.vocab_size * E * 2; launches++;

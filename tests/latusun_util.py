@@ -43,10 +43,15 @@ def configs(S):
         "shared_first": S.latusun_config(40, 64, [
             L(B, 2, 8, 4, 8, 8, experts=4, top=1, ff=32), L(B, 3, 4, 4, 16, 8, experts=None, kv_from=0), L(A, 2, 8, 8, 8, 8, experts=None),
             L(B, 2, 8, 4, 8, 8, experts=3, top=2, ff=20, kv_from=0)], residual_mult=0.7, logit_softcap=30.0),
-        # shapes the tcgen05 projections take in BF16 mode: width in whole 64-column tiles, fused projections of 384 and 256 rows
+        # shapes the tcgen05 projections and the tensor-core attention take in BF16 mode: width in whole 64-column tiles, fused
+    # projections of 384 and 256 rows, key size (unrotated + rotated) = value size = 64
         "tiles": S.latusun_config(128, 256, [
             L(A, 2, 48, 16, 64, 112, experts=4, top=2, ff=64, scaling=BLEND), L(B, 2, 48, 16, 64, 112, experts=4, top=1, ff=128),
             L(B, 2, 48, 16, 64, 112, experts=None, kv_from=1)], residual_mult=0.5),
+        # key size = value size = 128: the other instance of the tensor-core attention; a fused projection padded to whole tiles
+        "tiles128": S.latusun_config(128, 200, [
+            L(B, 2, 96, 32, 128, 64, experts=3, top=2, ff=64), L(A, 3, 96, 32, 128, 40, experts=None, scaling=BLEND),
+            L(B, 1, 96, 32, 128, 64, experts=2, top=1, ff=32, kv_from=0)], residual_mult=0.6, logit_softcap=12.0),
     }
 
 

@@ -42,7 +42,7 @@ def assert_rows(got, ref, tol, what=""):
 
 
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "shared_first", "tiles"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "shared_first", "tiles", "tiles128"])
 def test_every_layer_matches_oracle(pkg, name, compute):
     """Residual stream after every layer and the logits: norms, both mixer kinds, shared caches, routing, cap."""
     S, O = pkg.synth, oracle()
@@ -146,14 +146,18 @@ def test_portions_of_every_size(pkg, compute):
         plan.free()
 
 
+@pytest.mark.parametrize("name", ["tiles", "tiles128"])
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
-def test_tensor_core_projection_shapes(pkg, compute):
-    """Widths and fused projections in whole tiles of the tcgen05 GEMMs: a prompt of several row tiles, whole and in ragged
-    portions (one of them a single row), then decoded; experts that receive no row, one row, and more than a tile of rows."""
+def test_tensor_core_shapes(pkg, name, compute):
+    """Widths and fused projections in whole tiles of the tcgen05 GEMMs, key size = value size = 64 / 128 (in BF16 mode the prefill
+    expands keys and values per head and runs the tensor-core attention): a prompt of several row and key tiles, whole and in
+    ragged portions (one of them a single row), a portion AFTER decoded tokens (their cache rows come from the decode step),
+    then decoded; experts that receive no row, one row, and more than a tile of rows."""
     S, O = pkg.synth, oracle()
-    cfg = configs(S)["tiles"]
+    cfg = configs(S)[name]
     w = weights(S, cfg, 21, compute)
-    w["l1.mlp.router"][3] *= 0.0  # an expert whose score is always 1/2: next to never the largest
+    if name == "tiles":
+        w["l1.mlp.router"][3] *= 0.0  # an expert whose score is always 1/2: next to never the largest
     toks = np.random.default_rng(12).integers(0, cfg["vocab"], 230).tolist()
     ref = O.forward(cfg, w64(w), toks)
     assert compute == "float32" or min_margin(O, cfg, w, toks) > 0.2
@@ -161,7 +165,12 @@ def test_tensor_core_projection_shapes(pkg, compute):
     try:
         assert_rows(prefill_all(plan, toks, 100), ref, TOL[compute], "whole")
         got, p = [], 0
-        for m in (65, 2, 100, 1, 37):
+        for m in (65, 2, 100, 1, -3, 37):
+            if m < 0:
+                for _ in range(-m):
+                    got.append(plan.forward_decode(toks[p], p)[0][None])
+                    p += 1
+                continue
             got.append(prefill_all(plan, toks[p:p + m], 100, start=p))
             p += m
         while p < len(toks):
