@@ -26,6 +26,7 @@ struct BlockNormArgs {
     float emb_scale;
     const float *add_a;   // [n][E] (nullable): mixer output of the previous layer
     const float *add_b;   // [n * add_b_terms][E] (nullable): feed-forward results, row r owns entries r * terms .. r * terms + terms - 1
+    const int *add_b_map; // (nullable) entry e lives in row add_b_map[e] of add_b (results left in expert-sorted order)
     int add_b_terms;
     float add_mult;       // x += add_mult * (a + sum b)
     float *trace;         // [n][E]: copy of x after the update (nullable)
@@ -56,7 +57,10 @@ __global__ void __launch_bounds__(LY_NORM_THREADS) k_block_norm_rows(BlockNormAr
     if (a.add_a || a.add_b) {
         for (int i = tid; i < E; i += LY_NORM_THREADS) {
             float s = a.add_a ? a.add_a[src + i] : 0.0f;
-            for (int k = 0; k < a.add_b_terms; k++) s += a.add_b[((size_t)r * a.add_b_terms + k) * E + i];
+            for (int k = 0; k < a.add_b_terms; k++) {
+                const size_t e = (size_t)r * a.add_b_terms + k;
+                s += a.add_b[(a.add_b_map ? (size_t)a.add_b_map[e] : e) * E + i];
+            }
             row[i] = fmaf(a.add_mult, s, row[i]);
         }
     }
@@ -236,6 +240,46 @@ __global__ void __launch_bounds__(256) k_latent_spread(const bf16 *__restrict__ 
     if (i >= per * rows) return;
     const int j = (int)(i / per), h = (int)(i % per) / dr, e = (int)(i % per) % dr;
     KX[((size_t)j * heads + h) * (dk + dr) + dk + e] = cache16[(size_t)j * kw + rank + e];
+}
+
+// The same grouping for the tcgen05 projections: every expert's slots padded to whole 128-row tiles, so that a tile belongs to one
+// expert.  srt [max_tiles * 128]: slot of every padded row (-1: padding); slot_row [n_slots]: the inverse; row_scale: the slot's
+// routing weight (0 for padding); tile_group [max_tiles]: expert of every tile, -1 beyond the last.  Dynamic shared memory: 3 * experts ints.
+__global__ void __launch_bounds__(1024) k_moe_group_padded(const int *__restrict__ ids, const float *__restrict__ wts, int n_slots, int experts, int max_tiles,
+                                                           int *__restrict__ srt, int *__restrict__ slot_row, float *__restrict__ row_scale, int *__restrict__ tile_group) {
+    extern __shared__ int smi[];
+    int *count = smi, *offs = smi + experts, *cursor = smi + 2 * experts;
+    const int tid = threadIdx.x;
+    for (int e = tid; e < experts; e += 1024) count[e] = cursor[e] = 0;
+    for (int r = tid; r < max_tiles * 128; r += 1024) { srt[r] = -1; row_scale[r] = 0.0f; }
+    __syncthreads();
+    for (int s = tid; s < n_slots; s += 1024) atomicAdd(&count[ids[s]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int t = 0;
+        for (int e = 0; e < experts; e++) {
+            offs[e] = t * 128;
+            for (int b = 0; b < count[e] && t < max_tiles; b += 128) tile_group[t++] = e;
+        }
+        for (; t < max_tiles; t++) tile_group[t] = -1;
+    }
+    __syncthreads();
+    for (int s = tid; s < n_slots; s += 1024) {
+        const int e = ids[s], row = offs[e] + atomicAdd(&cursor[e], 1);
+        if (row < max_tiles * 128) { srt[row] = s; row_scale[row] = wts[s]; }
+        slot_row[s] = row;
+    }
+}
+
+// Rows of A (one per token) into expert-sorted order: padded row r reads token srt[r] / top; padding rows are zero.  E % 8 == 0.
+__global__ void __launch_bounds__(128) k_moe_gather(const bf16 *__restrict__ A, int E, int top, const int *__restrict__ srt, const int *__restrict__ tile_group,
+                                                    bf16 *__restrict__ AS) {
+    const int row = blockIdx.x;
+    if (tile_group[row >> 7] < 0) return;
+    const int slot = srt[row];
+    int4 *dst = reinterpret_cast<int4 *>(AS + (size_t)row * E);
+    const int4 *src = slot >= 0 ? reinterpret_cast<const int4 *>(A + (size_t)(slot / top) * E) : nullptr;
+    for (int i = threadIdx.x; i < E / 8; i += 128) dst[i] = src ? src[i] : make_int4(0, 0, 0, 0);
 }
 
 __global__ void __launch_bounds__(256) k_softcap(float *__restrict__ x, long long n, float cap) {

@@ -187,15 +187,16 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
     int nl = 0, rc;
     const float *pend_a = nullptr, *pend_b = nullptr;
     int pend_terms = 0;
+    const int *pend_map = nullptr;
     float *pend_trace = nullptr;
     auto bnorm = [&](bool embed, const float *w1, const float *b1, const float *w2, const float *b2) {
         ly::BlockNormArgs a = ly_block_norm_args(Y);
         a.emb = embed ? Y.emb : nullptr; a.tokens = tokens; a.st = st;
-        a.add_a = pend_a; a.add_b = pend_b; a.add_b_terms = pend_terms; a.trace = pend_trace;
+        a.add_a = pend_a; a.add_b = pend_b; a.add_b_terms = pend_terms; a.add_b_map = pend_map; a.trace = pend_trace;
         a.w1 = w1; a.b1 = b1; a.w2 = w2; a.b2 = b2;
         if (w1) { a.out1_32 = h16 ? nullptr : Y.A32; a.out1_16 = h16 ? Y.A16 : nullptr; }
         if (w2) { a.out2_32 = h16 ? nullptr : Y.A2_32; a.out2_16 = h16 ? Y.A2_16 : nullptr; }
-        pend_a = pend_b = nullptr; pend_terms = 0; pend_trace = nullptr;
+        pend_a = pend_b = nullptr; pend_terms = 0; pend_map = nullptr; pend_trace = nullptr;
         nl++;
         return launch_k(p, false, ly::k_block_norm_rows, dim3(n), dim3(LY_NORM_THREADS), (size_t)E * 4, a);
     };
@@ -285,6 +286,27 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
             nl++;
             if ((rc = launch_k(p, false, ly::k_moe_topk, dim3((n + 3) / 4), dim3(128), (size_t)0, (const float *)Y.ZR, n, X, top, Y.moe_ids, Y.moe_wts))) return rc;
             nl++;
+            if (h16 && Y.tc && L.tc_moe) {
+                // tcgen05 route: slots sorted by expert, every expert padded to whole 128-row tiles; the rows of LN2(x) are gathered
+                // into that order, the gate/up GEMM reads expert tile_group[m tile]'s rows of the stacked matrices and applies the
+                // routing weight and the activation in its epilogue, the down GEMM leaves its results in sorted order and the next
+                // block norm finds a slot's row through slot_row
+                int t128 = (n * top + 127) / 128 + X;
+                if (t128 > Y.max_tiles128) t128 = Y.max_tiles128;
+                if ((rc = launch_k(p, false, ly::k_moe_group_padded, dim3(1), dim3(1024), (size_t)3 * X * 4, (const int *)Y.moe_ids, (const float *)Y.moe_wts, n * top, X, t128, Y.srt, Y.slot_row,
+                                   Y.row_scale, Y.tile_group128))) return rc;
+                if ((rc = launch_k(p, false, ly::k_moe_gather, dim3(t128 * 128), dim3(128), (size_t)0, (const ly::bf16 *)Y.A2_16, E, top, (const int *)Y.srt, (const int *)Y.tile_group128, Y.AS16))) return rc;
+                const uint32_t fl = pg::FLAVOR_BF16 | (s.ff_act == B200_ACT_SILU ? pg::FLAVOR_SILU_BF16 : pg::FLAVOR_GELU_BF16);
+                int gr = pg::gemm_launch<pg::GEMM_GATEUP, pg::GEMM_STAGES>(Y.m_as, L.m_moe_gate, L.m_moe_up, Y.m_ysp, Y.HS16, F, t128 * 128, t128, F / (pg::BN / 2), E, p->stream, fl,
+                                                                         pg::Grouped{Y.tile_group128, 2 * F, Y.row_scale});
+                if (!gr) gr = pg::gemm_launch<pg::GEMM_F32, pg::GEMM_STAGES>(L.m_moe_h, L.m_moe_down, L.m_moe_down, Y.m_ysp, Y.YSP, E, t128 * 128, t128, E / pg::BN, F, p->stream, pg::FLAVOR_BF16,
+                                                                            pg::Grouped{Y.tile_group128, E, nullptr});
+                if (gr) return fail(p, B200_ERR_CUDA, "tensor-core expert GEMM launch failed (%d)", gr);
+                nl += 4;
+                pend_b = Y.YSP; pend_map = Y.slot_row; pend_terms = top;
+                pend_trace = trace ? trace + r * (size_t)Y.cap * E : nullptr;
+                continue;
+            }
             int tiles = 0;
             if (!decode) {
                 tiles = (n * top + 63) / 64 + X;

@@ -43,6 +43,8 @@ struct LyLayer {
     ly::bf16 *w_router = nullptr;
     // TMA descriptors of the tensor-core prefill (BF16 compute mode, shapes the tcgen05 GEMM tiles cover); *_ok = usable
     CUtensorMap m_proj, m_o, m_gate, m_up, m_down, m_att, m_h;
+    CUtensorMap m_moe_gate, m_moe_up, m_moe_down, m_moe_h; // mixture of experts on the tcgen05 GEMM: all experts' matrices in one map each
+    bool tc_moe = false;
     bool tc_proj = false, tc_o = false, tc_gu = false, tc_down = false;
 };
 struct LyRun {
@@ -80,6 +82,12 @@ struct Layered {
     ly::bf16 *A2_16 = nullptr, *QU16 = nullptr, *LAT16 = nullptr;
     ly::bf16 *KX16 = nullptr, *VX16 = nullptr; // keys / values of one layer expanded per head for a prefill chunk: [context][heads * size]
     int maxKX = 0, maxVX = 0, pf_pos = 0;      // pf_pos: first position of the chunk being enqueued
+    // expert-sorted, tile-padded operands of the tcgen05 expert projections (BF16 prefill)
+    ly::bf16 *AS16 = nullptr, *HS16 = nullptr;
+    float *YSP = nullptr, *row_scale = nullptr;
+    int *srt = nullptr, *slot_row = nullptr, *tile_group128 = nullptr;
+    int max_tiles128 = 0;
+    CUtensorMap m_as, m_ysp;
     int *moe_ids = nullptr, *moe_perm = nullptr, *tile_group = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr;
     int maxQ = 0, maxL = 0, maxQU = 0, maxTop = 0, maxExperts = 0, max_tiles = 0, max_att_dv = 1;
     std::vector<std::pair<std::vector<float>, float *>> rope_tables; // (key, device table)
@@ -320,6 +328,13 @@ static int ly_tc_init(b200_plan *p) {
             L.tc_down = fits(E, F) && pg::make_map(&L.m_down, L.w_down, E, F, 128) == 0 && pg::make_map(&L.m_h, Y.H16, rows, F, pg::BM) == 0;
         }
     }
+    if (Y.AS16 && pg::make_map(&Y.m_as, Y.AS16, (uint64_t)Y.max_tiles128 * 128, E, pg::BM) == 0 && pg::make_map_c(&Y.m_ysp, Y.YSP, (uint64_t)Y.max_tiles128 * 128, E) == 0)
+        for (LyLayer &L : Y.layers) {
+            if (L.s.ff_kind != B200_FF_MOE || L.s.ff_dim % 64) continue;
+            const uint64_t F = L.s.ff_dim, X = L.s.ff_experts;
+            L.tc_moe = pg::make_map(&L.m_moe_gate, L.w_gu, X * 2 * F, E, pg::BN / 2) == 0 && pg::make_map(&L.m_moe_up, L.w_gu + F * E, X * 2 * F - F, E, pg::BN / 2) == 0 &&
+                       pg::make_map(&L.m_moe_down, L.w_down, X * E, F, pg::BN) == 0 && pg::make_map(&L.m_moe_h, Y.HS16, (uint64_t)Y.max_tiles128 * 128, F, pg::BM) == 0;
+        }
     Y.tc_head = fits(V, E) && pg::make_map(&Y.m_head, Y.head, V, E, 128) == 0 && pg::make_map_c(&Y.m_log_c, Y.LOG, 256, V) == 0;
     Y.tc = true;
     return B200_OK;
@@ -596,6 +611,17 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if ((rc = dalloc(p, &Y.tile_group, (size_t)Y.max_tiles * 4))) return rc;
             if ((rc = dalloc(p, &Y.tile_row0, (size_t)Y.max_tiles * 4))) return rc;
             if ((rc = dalloc(p, &Y.tile_rows, (size_t)Y.max_tiles * 4))) return rc;
+            if (!Y.f32 && Y.cap > 1 && E % 128 == 0) { // expert projections of the BF16 prefill on the tcgen05 GEMM
+                Y.max_tiles128 = (int)((cap * slots + 127) / 128) + Y.maxExperts;
+                const size_t rowsP = (size_t)Y.max_tiles128 * 128;
+                if ((rc = dalloc(p, &Y.AS16, rowsP * E * 2))) return rc;
+                if ((rc = dalloc(p, &Y.HS16, rowsP * maxF * 2))) return rc;
+                if ((rc = dalloc(p, &Y.YSP, rowsP * E * 4))) return rc;
+                if ((rc = dalloc(p, &Y.row_scale, rowsP * 4))) return rc;
+                if ((rc = dalloc(p, &Y.srt, rowsP * 4))) return rc;
+                if ((rc = dalloc(p, &Y.slot_row, cap * slots * 4))) return rc;
+                if ((rc = dalloc(p, &Y.tile_group128, (size_t)Y.max_tiles128 * 4))) return rc;
+            }
             CK(cudaMemset(Y.moe_ids, 0, cap * slots * 4));
             CK(cudaMemset(Y.moe_wts, 0, cap * slots * 4));
         }

@@ -57,8 +57,22 @@ constexpr uint32_t UMMA_IDESC_AB_BF16 = (1u << 7) | (1u << 10);
 // Run-time flavour of a launch (one kernel serves the GGUF plans and the layered plans):
 //   FLAVOR_BF16       operands are BF16 instead of FP16 (same bytes per element, same TMA maps);
 //   FLAVOR_GELU_BF16  the gate/up epilogue emits bf16(gelu_tanh(g) * u) instead of f16(silu(g) * u).
-enum { FLAVOR_BF16 = 1u, FLAVOR_GELU_BF16 = 2u };
+//   FLAVOR_SILU_BF16  the gate/up epilogue emits bf16(silu(g) * u).
+enum { FLAVOR_BF16 = 1u, FLAVOR_GELU_BF16 = 2u, FLAVOR_SILU_BF16 = 4u };
+// Grouped rows (a mixture of experts; single-CTA kernel): the rows of A are sorted by group and every group is padded to whole
+// 128-row tiles, so an M tile belongs to ONE group: tile_group[m tile] (-1: no work) selects the weight matrix, whose rows start
+// b_rows * group further down the B tensor map(s).  row_scale (nullable) multiplies gate and up before the activation (a weight
+// on the expert's INPUT).  tile_group == nullptr: an ordinary GEMM.
+struct Grouped {
+    const int *tile_group;
+    int b_rows;
+    const float *row_scale;
+};
 __device__ __forceinline__ uint32_t gated_pair(uint32_t flavor, float g0, float g1, float u0, float u1) {
+    if (flavor & FLAVOR_SILU_BF16) {
+        const __nv_bfloat162 hh = __floats2bfloat162_rn((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+        return *reinterpret_cast<const uint32_t *>(&hh);
+    }
     if (flavor & FLAVOR_GELU_BF16) {
         const float t0 = 0.7978845608028654f * fmaf(0.044715f * g0 * g0, g0, g0), t1 = 0.7978845608028654f * fmaf(0.044715f * g1 * g1, g1, g1);
         const __nv_bfloat162 hh = __floats2bfloat162_rn(0.5f * g0 * (1.0f + tanhf(t0)) * u0, 0.5f * g1 * (1.0f + tanhf(t1)) * u1);
@@ -101,8 +115,10 @@ template <int STAGES> constexpr size_t smem_bytes() { return (size_t)STAGES * (B
 template <int MODE, int STAGES>
 __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                                                          const __grid_constant__ CUtensorMap tma_b2, const __grid_constant__ CUtensorMap tma_c,
-                                                         void *__restrict__ Cv, int ldc, int m_valid, int K, uint32_t flavor) {
+                                                         void *__restrict__ Cv, int ldc, int m_valid, int K, uint32_t flavor, Grouped gr) {
     extern __shared__ uint8_t smem_raw[];
+    const int grp = gr.tile_group ? gr.tile_group[blockIdx.x] : 0;
+    if (grp < 0) return; // a tile without rows: the whole CTA leaves before it owns a barrier or tensor memory
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023); // SWIZZLE_128B tiles need 1024-byte alignment
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     static_assert(STAGES * (A_BYTES + B_BYTES) >= BM * BN * 4, "the C tile is staged in the operand ring");
@@ -127,6 +143,7 @@ __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
     const int nk = (K + BK - 1) / BK, m0 = blockIdx.x * BM;
     const int n0 = blockIdx.y * (MODE == GEMM_GATEUP ? BN / 2 : BN);
+    const int nb = n0 + grp * gr.b_rows; // row of this tile's weights in the B tensor map(s)
 
     if (warp == 0 && lane == 0) {
         // ===== TMA producer =====
@@ -136,10 +153,10 @@ __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant_
             mbar_expect_tx(full0 + 8 * st, A_BYTES + B_BYTES);
             tma_load_2d(s32(sA + st * A_BYTES), &tma_a, kb * BK, m0, full0 + 8 * st);
             if (MODE == GEMM_GATEUP) {
-                tma_load_2d(s32(sB + st * B_BYTES), &tma_b, kb * BK, n0, full0 + 8 * st);
-                tma_load_2d(s32(sB + st * B_BYTES + B_BYTES / 2), &tma_b2, kb * BK, n0, full0 + 8 * st);
+                tma_load_2d(s32(sB + st * B_BYTES), &tma_b, kb * BK, nb, full0 + 8 * st);
+                tma_load_2d(s32(sB + st * B_BYTES + B_BYTES / 2), &tma_b2, kb * BK, nb, full0 + 8 * st);
             } else {
-                tma_load_2d(s32(sB + st * B_BYTES), &tma_b, kb * BK, n0, full0 + 8 * st);
+                tma_load_2d(s32(sB + st * B_BYTES), &tma_b, kb * BK, nb, full0 + 8 * st);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -173,13 +190,14 @@ __global__ void __launch_bounds__(256) k_gemm_f16_tcgen05(const __grid_constant_
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row < m_valid) {
                     uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)row * ldc + n0 + c0);
+                    const float sc = gr.row_scale ? gr.row_scale[row] : 1.0f;
 #pragma unroll
                     for (int v = 0; v < 4; v++) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
-                            const float g0 = __uint_as_float(g[8 * v + 2 * e]), g1 = __uint_as_float(g[8 * v + 2 * e + 1]);
-                            w[e] = gated_pair(flavor, g0, g1, __uint_as_float(u[8 * v + 2 * e]), __uint_as_float(u[8 * v + 2 * e + 1]));
+                            const float g0 = __uint_as_float(g[8 * v + 2 * e]) * sc, g1 = __uint_as_float(g[8 * v + 2 * e + 1]) * sc;
+                            w[e] = gated_pair(flavor, g0, g1, __uint_as_float(u[8 * v + 2 * e]) * sc, __uint_as_float(u[8 * v + 2 * e + 1]) * sc);
                         }
                         dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
@@ -641,13 +659,13 @@ inline int make_map_c(CUtensorMap *map, const void *base, uint64_t rows, uint64_
 
 template <int MODE, int STAGES>
 inline int gemm_launch(const CUtensorMap &a, const CUtensorMap &b, const CUtensorMap &b2, const CUtensorMap &c, void *C, int ldc, int m_valid, int m_tiles,
-                       int n_tiles, int K, cudaStream_t stream, uint32_t flavor = 0) {
+                       int n_tiles, int K, cudaStream_t stream, uint32_t flavor = 0, Grouped gr = Grouped{nullptr, 0, nullptr}) {
     static bool attr = false; // one flag per instantiation
     if (!attr) {
         if (cudaFuncSetAttribute(k_gemm_f16_tcgen05<MODE, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<STAGES>()) != cudaSuccess) return -4;
         attr = true;
     }
-    k_gemm_f16_tcgen05<MODE, STAGES><<<dim3(m_tiles, n_tiles), 256, smem_bytes<STAGES>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, flavor);
+    k_gemm_f16_tcgen05<MODE, STAGES><<<dim3(m_tiles, n_tiles), 256, smem_bytes<STAGES>(), stream>>>(a, b, b2, c, C, ldc, m_valid, K, flavor, gr);
     return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
