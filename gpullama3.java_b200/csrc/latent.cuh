@@ -6,7 +6,7 @@
 //   * k_latent_prep      latent attention: RMS norm of the key/value latent, rotation of the shared key part and of every
 //                        head's rotated query part (table-driven: half-split or interleaved pairs, any blend of frequencies),
 //                        cache write [latent | rotated shared key part];
-//   * k_moe_topk         sigmoid of the router logits (an FP32 projection) and selection of the `top` largest per row;
+//   * k_moe_route        router logits in FP32, sigmoid scores and selection of the `top` largest per row;
 //   * k_moe_group        slots sorted by expert into tiles of 64 for the grouped projection kernels (GemmView);
 //   * k_softcap          x <- cap * tanh(x / cap) over a logits buffer.
 // The latent attention itself runs through k_window_attention: with W_uk folded into the query (q' = W_uk^T q_u per head)
@@ -173,29 +173,76 @@ __global__ void __launch_bounds__(256) k_latent_prep(float *__restrict__ P, int 
 // ---------------------------------------------------------------------------------------------------------------------
 // Mixture of experts: router and grouping.
 // ---------------------------------------------------------------------------------------------------------------------
-// Router logits z [n][experts] come from the projection kernels (FP32 accumulation).  One warp per row: s_e = sigmoid(z_e), then
-// the `top` largest (the lowest index wins a tie); ids / wts [n][top], in order of falling score.
-__global__ void __launch_bounds__(128) k_moe_topk(const float *__restrict__ Z, int n, int experts, int top, int *__restrict__ ids, float *__restrict__ wts) {
-    const int lane = threadIdx.x & 31, r = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (r >= n) return;
-    const float *z = Z + (size_t)r * experts;
-    unsigned long long taken_lo = 0ull; // experts this lane has given away, by (e / 32): lanes own e = lane, lane + 32, ...
+// Router: logits z_e = <Wr[e], x> accumulated in FP32 (x FP32 or its BF16 rounding, Wr BF16), scores s_e = sigmoid(z_e), then the
+// `top` largest (the lowest index wins a tie); ids / wts [n][top] in order of falling score.  Four warps per CTA: with
+// rows_per_cta == 4 every warp owns a row (prefill chunks: the router matrix is small and stays in L1 / L2), with
+// rows_per_cta == 1 the four warps share the experts of one row.  Dynamic shared memory: rows_per_cta * (E + experts) floats.
+template <typename IN_T>
+__global__ void __launch_bounds__(128) k_moe_route(const IN_T *__restrict__ X, const bf16 *__restrict__ Wr, int n, int E, int experts, int top, int rows_per_cta,
+                                                   int *__restrict__ ids, float *__restrict__ wts) {
+    extern __shared__ __align__(16) float sm[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool shared_row = rows_per_cta == 1;
+    const int r = shared_row ? blockIdx.x : blockIdx.x * 4 + warp;
+    float *xs = sm + (shared_row ? 0 : (size_t)warp * E), *z = sm + (size_t)rows_per_cta * E + (shared_row ? 0 : (size_t)warp * experts);
+    if (r < n) {
+        if (shared_row) for (int i = tid; i < E; i += 128) xs[i] = (float)X[(size_t)r * E + i];
+        else for (int i = lane; i < E; i += 32) xs[i] = (float)X[(size_t)r * E + i];
+    }
+    if (shared_row) __syncthreads(); else __syncwarp();
+    if (r < n) {
+        const bool vec = (E & 7) == 0 && (((size_t)Wr) & 15) == 0;
+        for (int e = shared_row ? warp : 0; e < experts; e += shared_row ? 4 : 1) {
+            const float acc = dot_row_bf16(Wr + (size_t)e * E, xs, E, lane, vec); // 128-bit weight loads, FP32 accumulation
+            if (lane == 0) z[e] = acc;
+        }
+    }
+    if (shared_row) __syncthreads(); else __syncwarp();
+    if (r >= n || (shared_row && warp != 0)) return;
     for (int k = 0; k < top; k++) {
         float best = -INFINITY;
         int bi = experts;
-        for (int e = lane, i = 0; e < experts; e += 32, i++)
-            if (!((taken_lo >> (i & 63)) & 1ull) && z[e] > best) { best = z[e]; bi = e; }
+        for (int e = lane; e < experts; e += 32)
+            if (z[e] > best) { best = z[e]; bi = e; }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
-        if ((bi & 31) == lane && bi < experts) taken_lo |= 1ull << ((bi >> 5) & 63);
         if (lane == 0) {
             ids[(size_t)r * top + k] = bi < experts ? bi : 0;
             wts[(size_t)r * top + k] = 1.0f / (1.0f + expf(-best));
+            if (bi < experts) z[bi] = -INFINITY; // taken
         }
+        __syncwarp();
+    }
+}
+
+// The decode step spreads the router's rows over several CTAs (k_matvec_bf16) and selects here: one warp, logits z [experts]
+// in, the `top` largest sigmoid scores out.  Dynamic shared memory: experts floats.
+__global__ void __launch_bounds__(32) k_moe_topk(const float *__restrict__ Z, int experts, int top, int *__restrict__ ids, float *__restrict__ wts) {
+    extern __shared__ __align__(16) float z[];
+    const int lane = threadIdx.x;
+    for (int e = lane; e < experts; e += 32) z[e] = Z[e];
+    __syncwarp();
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int bi = experts;
+        for (int e = lane; e < experts; e += 32)
+            if (z[e] > best) { best = z[e]; bi = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) {
+            ids[k] = bi < experts ? bi : 0;
+            wts[k] = 1.0f / (1.0f + expf(-best));
+            if (bi < experts) z[bi] = -INFINITY;
+        }
+        __syncwarp();
     }
 }
 

@@ -282,10 +282,18 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
         pend_a = Y.Y;
         if (moe) {
             const int F = s.ff_dim, X = s.ff_experts, top = s.ff_top;
-            if ((rc = ly_project<ly::EPI_STORE>(p, decode, n, Y.A2_32, Y.A2_16, L.w_router, nullptr, X, E, Y.ZR, nullptr, X, 0))) return rc;
-            nl++;
-            if ((rc = launch_k(p, false, ly::k_moe_topk, dim3((n + 3) / 4), dim3(128), (size_t)0, (const float *)Y.ZR, n, X, top, Y.moe_ids, Y.moe_wts))) return rc;
-            nl++;
+            if (decode) { // one row: the router's rows stream through the multi-CTA matvec, one warp selects
+                if ((rc = ly_project<ly::EPI_STORE>(p, true, 1, Y.A2_32, nullptr, L.w_router, nullptr, X, E, Y.ZR, nullptr, X, 0))) return rc;
+                if ((rc = launch_k(p, false, ly::k_moe_topk, dim3(1), dim3(32), (size_t)X * 4, (const float *)Y.ZR, X, top, Y.moe_ids, Y.moe_wts))) return rc;
+                nl += 2;
+            } else {
+                const int rpc = n == 1 ? 1 : 4;
+                const size_t rsm = (size_t)rpc * (E + X) * 4;
+                if (h16) rc = launch_k(p, false, ly::k_moe_route<ly::bf16>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const ly::bf16 *)Y.A2_16, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts);
+                else rc = launch_k(p, false, ly::k_moe_route<float>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const float *)Y.A2_32, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts);
+                if (rc) return rc;
+                nl++;
+            }
             if (h16 && Y.tc && L.tc_moe) {
                 // tcgen05 route: slots sorted by expert, every expert padded to whole 128-row tiles; the rows of LN2(x) are gathered
                 // into that order, the gate/up GEMM reads expert tile_group[m tile]'s rows of the stacked matrices and applies the

@@ -11,6 +11,9 @@
 //   * k_qk_prep         whole-projection RMS norm of q and of k (one statistic over ALL heads), K / V rows into the window ring;
 //   * k_window_attention  sliding-window attention over a ring cache with a soft logit cap, a learned bucketed distance bias
 //                       and a softmax whose denominator carries an extra exp(0) (a value-less sink), sigmoid output gate.
+// The projection kernels take optional operand VIEWS (MvView / GemmView): a row stride for A, per-head batches, grouped rows for a
+// mixture of experts, an input scale and a sigmoid-gate epilogue; the attention kernels take row strides for the key and value
+// caches, so one cached row can serve as key and value (latent attention, latent.cuh).
 // Everything the residual, the norms and the softmax touch is FP32; explicit fmaf keeps fused multiply-adds although the
 // translation unit is compiled with -fmad=false for the bit-exact GGUF kernels.
 #pragma once

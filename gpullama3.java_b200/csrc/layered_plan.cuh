@@ -387,7 +387,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             if ((rc = ly_latent_sizes(p, l, L, c.n_layers, specs))) return rc;
             if (s.ff_kind != B200_FF_NONE && s.ff_kind != B200_FF_MOE) return fail(p, B200_ERR_UNSUPPORTED, "layer %d: feed-forward kind %d in a parallel block", l, s.ff_kind);
             if (s.ff_kind == B200_FF_MOE) {
-                if (s.ff_dim <= 0 || s.ff_experts <= 0 || s.ff_experts > 2048 || s.ff_top <= 0 || s.ff_top > s.ff_experts || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU))
+                if (s.ff_dim <= 0 || s.ff_experts <= 0 || (size_t)4 * (E + s.ff_experts) * 4 > (size_t)Y.smem_max || s.ff_top <= 0 || s.ff_top > s.ff_experts || (s.ff_act != B200_ACT_GELU_TANH && s.ff_act != B200_ACT_SILU))
                     return fail(p, B200_ERR_BAD_ARG, "layer %d: %d experts of width %d, %d chosen, activation %d", l, s.ff_experts, s.ff_dim, s.ff_top, s.ff_act);
                 if (s.ff_dim > Y.maxF) Y.maxF = s.ff_dim;
                 if (s.ff_top > Y.maxTop) Y.maxTop = s.ff_top;
@@ -429,6 +429,8 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (!attrs) {
             CK(set_max_dyn(ly::k_norm_rows, Y.smem_max));
             CK(set_max_dyn(ly::k_block_norm_rows, Y.smem_max));
+            CK(set_max_dyn(ly::k_moe_route<float>, Y.smem_max));
+            CK(set_max_dyn(ly::k_moe_route<ly::bf16>, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_STORE>, Y.smem_max));
             CK(set_max_dyn(ly::k_matvec_bf16<ly::EPI_GATED>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention<float>, Y.smem_max));
@@ -604,7 +606,7 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (Y.maxTop > 0) {
             Y.max_tiles = (int)((cap * slots + 63) / 64) + Y.maxExperts;
             if ((rc = dalloc(p, &Y.YS, cap * slots * E * 4))) return rc;
-            if ((rc = dalloc(p, &Y.ZR, cap * Y.maxExperts * 4))) return rc;
+            if ((rc = dalloc(p, &Y.ZR, (size_t)Y.maxExperts * 4))) return rc;
             if ((rc = dalloc(p, &Y.moe_ids, cap * slots * 4))) return rc;
             if ((rc = dalloc(p, &Y.moe_wts, cap * slots * 4))) return rc;
             if ((rc = dalloc(p, &Y.moe_perm, cap * slots * 4))) return rc;
