@@ -183,9 +183,9 @@ def compare_layered(pkg, lb, local: int, steps: int, warmup: int, sizes):
 # key/value head per four query heads, and a dense feed-forward as wide as the experts one token uses (top x expert width).
 LATUSUN_SIZES = {
     # name: (width, heads, unrotated, rotated, value, latent, experts, top, expert ff, vocab, layers)
-    # (unrotated + rotated = value = 64 / 128, so the closest model runs its tensor-core attention)
+    # (key sizes unrotated + rotated = 64 / 192 with value sizes 64 / 128: instances of the tensor-core attention both designs run)
     "small": (1024, 8, 48, 16, 64, 256, 8, 2, 1024, 32768, 4),
-    "lite-like": (2048, 16, 96, 32, 128, 512, 16, 4, 1408, 32768, 4),
+    "lite-like": (2048, 16, 128, 64, 128, 512, 16, 4, 1408, 32768, 4),
 }
 
 

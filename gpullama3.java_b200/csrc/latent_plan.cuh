@@ -8,7 +8,7 @@
 //   -> W_uk folded into the query, one product per head                    (batched matvec / GEMM over blockIdx.y / z)
 //   -> attention over the cached rows [latent | shared key part]            (k_window_attention, one key/value head for all query heads)
 //   -> W_uv per head on the attention's latent-space output, times the sigmoid gate
-//      (BF16 prefill of layers whose key size = value size = 64 / 128 instead: keys and values expanded per head for the chunk,
+//      (BF16 prefill of layers whose (key, value) size is (64, 64), (128, 128) or (192, 128) instead: keys and values expanded per head for the chunk,
 //       tensor-core attention kernel with the gate in its epilogue)
 //   -> output projection
 //   -> router -> (prefill: slots grouped by expert) -> gated expert projection -> expert down projection, one result row per slot.
@@ -219,7 +219,7 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
         if ((rc = launch_k(p, false, ly::k_latent_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, la, R.kc, R.own ? R.kc16 : (ly::bf16 *)nullptr, Y.ring, Y.Q, h16 ? Y.QU16 : nullptr, st))) return rc;
         nl++;
         if (h16 && L.expand && R.kc16) {
-            // BF16 prefill, key size = value size = 64 / 128: keys and values of every cached position up to the chunk's end are
+            // BF16 prefill, (key, value) size an instance of the tensor-core attention: keys and values of every cached position up to the chunk's end are
             // expanded per head (two GEMMs over the BF16 twin of the cache), the rotated shared part is copied behind each head's
             // key, and the tensor-core attention kernel reads [q_u | rot q_r] from the projection rows; gate in its epilogue
             const int DK = s.key_dim + s.rot_dim, M = Y.pf_pos + n;
@@ -235,11 +235,8 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
             ly::WindowAttn wa{};
             wa.heads = wa.kv_heads = s.heads; wa.dk = DK; wa.dv = s.value_dim; wa.window = s.window; wa.ring = Y.ring; wa.ldk = s.heads * DK; wa.ldv = L.gd;
             wa.scale = s.score_scale; wa.gate = s.gate; wa.gate_off = L.g_off - L.q_off; wa.eps = Y.c.norm_eps;
-            const dim3 grid((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, s.heads);
-            if (DK == 64) rc = launch_k(p, false, ly::k_window_attention_mma<64, 64>, grid, dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<64, 64>(s.window), (const float *)(Y.PROJ + L.q_off),
-                                        Y.maxP, wa, (const ly::bf16 *)Y.KX16, (const ly::bf16 *)Y.VX16, st, n, Y.ATT16, L.gd);
-            else rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, grid, dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(s.window), (const float *)(Y.PROJ + L.q_off),
-                               Y.maxP, wa, (const ly::bf16 *)Y.KX16, (const ly::bf16 *)Y.VX16, st, n, Y.ATT16, L.gd);
+            rc = ly_launch_mma(p, ly_mma_kind(DK, s.value_dim), n, s.heads, s.window, (const float *)(Y.PROJ + L.q_off), Y.maxP, wa, (const ly::bf16 *)Y.KX16, (const ly::bf16 *)Y.VX16, st,
+                               Y.ATT16, L.gd);
             if (rc) return rc;
             nl += 4;
         } else {

@@ -648,7 +648,8 @@ __global__ void __launch_bounds__(LY_ATT_THREADS) k_window_attention(const float
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// The same attention for a prefill chunk on the tensor cores (BF16 compute mode): one CTA per (128 query rows, head), eight
+// The same attention for a prefill chunk on the tensor cores (BF16 compute mode; instantiated for key / value sizes 64 / 64,
+// 128 / 128 and 192 / 128): one CTA per (128 query rows, head), eight
 // warps of 16 rows (two warps per scheduler: a lone warp cannot hide the latency of its own dependent instructions).  Keys and values come from the BF16 twin rows of the ring (written by k_qk_prep next to the FP32 rows the
 // decode step reads): key tiles of 64 positions travel global -> shared with cp.async, double buffered, so the copy of tile
 // i + 1 overlaps the mma.sync m16n8k16 work on tile i; V fragments are read with ldmatrix.trans.  Scores, cap, distance bias,

@@ -151,6 +151,20 @@ static size_t ly_att_smem(const b200_layer_spec &s, int ring) {
     return ly_att_smem(s.mixer == B200_MIXER_LATENT_ATTENTION ? s.kv_rank + s.rot_dim : s.key_dim, s.window);
 }
 
+// Instances of the tensor-core prefill attention: (key size, value size) = (64, 64), (128, 128), (192, 128); 0 = none.
+static int ly_mma_kind(int dk, int dv) { return dk == 64 && dv == 64 ? 1 : dk == 128 && dv == 128 ? 2 : dk == 192 && dv == 128 ? 3 : 0; }
+static size_t ly_mma_smem(int kind, int window) {
+    return kind == 1 ? ly::att_mma_smem_bytes<64, 64>(window) : kind == 2 ? ly::att_mma_smem_bytes<128, 128>(window) : ly::att_mma_smem_bytes<192, 128>(window);
+}
+static int ly_launch_mma(b200_plan *p, int kind, int n, int heads, int window, const float *P, int ldp, const ly::WindowAttn &wa, const ly::bf16 *k16, const ly::bf16 *v16,
+                         const StepState *st, ly::bf16 *out, int ldo) {
+    const dim3 grid((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, heads), block(LY_ATT_MMA_THREADS);
+    const size_t sm = ly_mma_smem(kind, window);
+    if (kind == 1) return launch_k(p, false, ly::k_window_attention_mma<64, 64>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
+    if (kind == 2) return launch_k(p, false, ly::k_window_attention_mma<128, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
+    return launch_k(p, false, ly::k_window_attention_mma<192, 128>, grid, block, sm, P, ldp, wa, k16, v16, st, n, out, ldo);
+}
+
 static ly::WindowAttn ly_attn_args(const Layered &Y, const LyLayer &L) {
     ly::WindowAttn a{};
     a.heads = L.s.heads; a.kv_heads = L.s.kv_heads; a.dk = L.s.key_dim; a.dv = L.s.value_dim;
@@ -245,13 +259,9 @@ static int ly_enqueue(b200_plan *p, bool decode, int n, const StepState *st, con
         if ((rc = launch_k(p, false, ly::k_qk_prep, dim3(n), dim3(256), (size_t)0, Y.PROJ, Y.maxP, wa, (const float *)L.b_proj, R.kc, R.vc, R.kc16, R.vc16, st))) return rc;
         nl++;
         const size_t asm_ = ly_att_smem(L.s, Y.ring);
-        const bool mma64 = L.s.key_dim == 64 && L.s.value_dim == 64, mma128 = L.s.key_dim == 128 && L.s.value_dim == 128;
-        if (h16 && R.kc16 && mma64)
-            rc = launch_k(p, false, ly::k_window_attention_mma<64, 64>, dim3((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<64, 64>(L.s.window),
-                          (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, n, Y.ATT16, L.gd);
-        else if (h16 && R.kc16 && mma128)
-            rc = launch_k(p, false, ly::k_window_attention_mma<128, 128>, dim3((n + LY_ATT_MMA_ROWS - 1) / LY_ATT_MMA_ROWS, L.s.heads), dim3(LY_ATT_MMA_THREADS), ly::att_mma_smem_bytes<128, 128>(L.s.window),
-                          (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, n, Y.ATT16, L.gd);
+        const int mma = ly_mma_kind(L.s.key_dim, L.s.value_dim);
+        if (h16 && R.kc16 && mma)
+            rc = ly_launch_mma(p, mma, n, L.s.heads, L.s.window, (const float *)Y.PROJ, Y.maxP, wa, (const ly::bf16 *)R.kc16, (const ly::bf16 *)R.vc16, st, Y.ATT16, L.gd);
         else if (h16) rc = launch_k(p, false, ly::k_window_attention<ly::bf16>, dim3(n, L.s.heads), dim3(LY_ATT_THREADS), asm_, (const float *)Y.PROJ, Y.maxP, wa,
                                (const float *)R.kc, (const float *)R.vc, st, Y.ATT16, L.gd, ly::KeySplit{nullptr, nullptr, nullptr});
         else {
@@ -437,17 +447,17 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
             CK(set_max_dyn(ly::k_window_attention<ly::bf16>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention_mma<64, 64>, Y.smem_max));
             CK(set_max_dyn(ly::k_window_attention_mma<128, 128>, Y.smem_max));
+            CK(set_max_dyn(ly::k_window_attention_mma<192, 128>, Y.smem_max));
             attrs = true;
         }
     }
-    // Latent attention, BF16 prefill: layers whose per-head key size (unrotated + rotated) equals their value size, 64 or 128, expand
-    // keys and values per head for the chunk and run the tensor-core attention kernel; all others attend in the folded form
+    // Latent attention, BF16 prefill: layers whose per-head key size (unrotated + rotated) and value size are an instance of the
+    // tensor-core attention kernel expand keys and values per head for the chunk and run it; all others attend in the folded form
     if (par && !Y.f32 && Y.att_mma && Y.cap > 1 && Y.maxP % 4 == 0)
         for (LyLayer &L : Y.layers) {
             const int DK = L.s.key_dim + L.s.rot_dim;
-            const bool s64 = DK == 64 && L.s.value_dim == 64, s128 = DK == 128 && L.s.value_dim == 128;
-            const size_t need = s64 ? ly::att_mma_smem_bytes<64, 64>(L.s.window) : ly::att_mma_smem_bytes<128, 128>(L.s.window);
-            L.expand = (s64 || s128) && need <= (size_t)Y.smem_max && (!L.s.gate || L.g_off % 2 == 0) && L.s.key_dim % 8 == 0;
+            const int kind = ly_mma_kind(DK, L.s.value_dim);
+            L.expand = kind && ly_mma_smem(kind, L.s.window) <= (size_t)Y.smem_max && (!L.s.gate || L.g_off % 2 == 0) && L.s.key_dim % 8 == 0;
             if (L.expand) {
                 if (L.s.heads * DK > Y.maxKX) Y.maxKX = L.s.heads * DK;
                 if (L.gd > Y.maxVX) Y.maxVX = L.gd;
@@ -563,9 +573,8 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         CK(cudaMemset(R.kc, 0, (size_t)Y.ring * L.kd * 4));
         CK(cudaMemset(R.vc, 0, (size_t)Y.ring * L.vd * 4));
         // tensor-core prefill attention: BF16 plans, key = value size 64 or 128, a window whose tiles fit shared memory
-        const bool s64 = L.s.key_dim == 64 && L.s.value_dim == 64, s128 = L.s.key_dim == 128 && L.s.value_dim == 128;
-        const size_t need = s64 ? ly::att_mma_smem_bytes<64, 64>(L.s.window) : ly::att_mma_smem_bytes<128, 128>(L.s.window);
-        if (!Y.f32 && Y.att_mma && Y.cap > 1 && (s64 || s128) && need <= (size_t)Y.smem_max && Y.maxP % 4 == 0) {
+        const int kind = ly_mma_kind(L.s.key_dim, L.s.value_dim);
+        if (!Y.f32 && Y.att_mma && Y.cap > 1 && kind && ly_mma_smem(kind, L.s.window) <= (size_t)Y.smem_max && Y.maxP % 4 == 0) {
             if ((rc = dalloc(p, &R.kc16, (size_t)Y.ring * L.kd * 2))) return rc;
             if ((rc = dalloc(p, &R.vc16, (size_t)Y.ring * L.vd * 2))) return rc;
             CK(cudaMemset(R.kc16, 0, (size_t)Y.ring * L.kd * 2));

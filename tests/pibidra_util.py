@@ -50,6 +50,7 @@ def configs(S):
         # shapes the tensor-core prefill kernels take (head sizes 64 / 128, widths in whole GEMM tiles), windows that end inside a key tile
         "tiles64": (S.pibidra_config(128, 256, [L(2, 1, 64, 64, 70, 256, bias_max=100.0), L(2, 1, 64, 64, 9, 256)], loop=(0, 2, 2)), 14),
         "tiles128": (S.pibidra_config(256, 384, [L(2, 2, 128, 128, 33, 128, bias_max=40.0), L(2, 1, 128, 128, 129, 384, bias_max=200.0)]), 8),
+        "tiles192": (S.pibidra_config(128, 256, [L(2, 1, 192, 128, 77, 128, bias_max=90.0), L(2, 2, 192, 128, 20, 256, bias_max=30.0)]), 10),
     }
 
 

@@ -42,7 +42,7 @@ def assert_rows(got, ref, tol, what=""):
 
 
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "shared_first", "tiles", "tiles128"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "shared_first", "tiles", "tiles128", "tiles192"])
 def test_every_layer_matches_oracle(pkg, name, compute):
     """Residual stream after every layer and the logits: norms, both mixer kinds, shared caches, routing, cap."""
     S, O = pkg.synth, oracle()
@@ -146,10 +146,10 @@ def test_portions_of_every_size(pkg, compute):
         plan.free()
 
 
-@pytest.mark.parametrize("name", ["tiles", "tiles128"])
+@pytest.mark.parametrize("name", ["tiles", "tiles128", "tiles192"])
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
 def test_tensor_core_shapes(pkg, name, compute):
-    """Widths and fused projections in whole tiles of the tcgen05 GEMMs, key size = value size = 64 / 128 (in BF16 mode the prefill
+    """Widths and fused projections in whole tiles of the tcgen05 GEMMs, (key, value) sizes (64, 64), (128, 128), (192, 128) (in BF16 mode the prefill
     expands keys and values per head and runs the tensor-core attention): a prompt of several row and key tiles, whole and in
     ragged portions (one of them a single row), a portion AFTER decoded tokens (their cache rows come from the decode step),
     then decoded; experts that receive no row, one row, and more than a tile of rows."""

@@ -101,7 +101,7 @@ def test_portions_of_every_size(pkg, compute):
         plan.free()
 
 
-@pytest.mark.parametrize("name", ["tiles64", "tiles128"])
+@pytest.mark.parametrize("name", ["tiles64", "tiles128", "tiles192"])
 @pytest.mark.parametrize("compute", ["float32", "bfloat16"])
 def test_tensor_core_prefill_shapes(pkg, name, compute):
     """Head sizes and widths that take the tcgen05 GEMMs and the tensor-core attention in BF16 mode: a prompt longer than
