@@ -26,7 +26,8 @@ def oracle():
 def configs(S):
     """name -> config.  Sizes differ from one another on purpose: head counts 1 .. 5, unequal key / rotated / value / latent
     sizes, sizes that are no multiple of 4 or 8, one expert and all experts chosen, layers without feed-forward, a rotation
-    over only part of the rotated entries, cache sharing over one and over two layers, both mixer kinds in both orders."""
+    over only part of the rotated entries, blended frequencies on either mixer kind and on neither, cache sharing over one and
+    over two layers, both mixer kinds in both orders."""
     A, B = "latent_attention", "latent_attention_2"
     L = S.latusun_layer
     return {
@@ -41,8 +42,8 @@ def configs(S):
             L(A, 1, 9, 2, 3, 5, experts=1, top=1, ff=13, scaling={"factor": 2.0, "original": 16, "fast": 4.0, "slow": 0.5})],
             eps=1e-5, residual_mult=1.0, logit_softcap=None),
         "shared_first": S.latusun_config(40, 64, [
-            L(B, 2, 8, 4, 8, 8, experts=4, top=1, ff=32), L(B, 3, 4, 4, 16, 8, experts=None, kv_from=0), L(A, 2, 8, 8, 8, 8, experts=None),
-            L(B, 2, 8, 4, 8, 8, experts=3, top=2, ff=20, kv_from=0)], residual_mult=0.7, logit_softcap=30.0),
+            L(B, 2, 8, 4, 8, 8, experts=4, top=1, ff=32, scaling=BLEND), L(B, 3, 4, 4, 16, 8, experts=None, kv_from=0, scaling=BLEND),
+            L(A, 2, 8, 8, 8, 8, experts=None), L(B, 2, 8, 4, 8, 8, experts=3, top=2, ff=20, kv_from=0, scaling=BLEND)], residual_mult=0.7, logit_softcap=30.0),
         # shapes the tcgen05 projections and the tensor-core attention take in BF16 mode: width in whole 64-column tiles, fused
     # projections of 384 and 256 rows, key size (unrotated + rotated) = value size = 64
         "tiles": S.latusun_config(128, 256, [
