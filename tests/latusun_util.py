@@ -121,3 +121,41 @@ def min_margin(O, cfg, w, toks):
     m = []
     O.forward(cfg, w64(w), toks, margins=m)
     return min(m) if m else np.inf
+
+
+def random_config(S, rng):
+    """A random model: 1-6 layers of either kind in any order, random head counts and sizes (incl. the tensor-core shapes), rotation
+    over all or part of the rotated entries with or without blended frequencies, cache readers, 1-33 experts with 1-4 chosen or no
+    feed-forward, random constants."""
+    A, B = "latent_attention", "latent_attention_2"
+    E = int(rng.choice([24, 40, 64, 96, 128, 192, 256, 320]))
+    V = int(rng.integers(30, 400))
+    layers, owners = [], []
+    for i in range(int(rng.integers(1, 7))):
+        kind = A if rng.random() < 0.5 else B
+        H, dk, dr = int(rng.choice([1, 2, 3, 4, 6, 8])), int(rng.choice([4, 8, 12, 16, 32, 48, 64, 96, 128])), int(rng.choice([2, 4, 8, 16, 32, 64]))
+        dv, R = int(rng.choice([4, 8, 20, 32, 64, 80, 128])), int(rng.choice([4, 8, 16, 24, 64, 112, 128]))
+        if rng.random() < 0.3 and dk + dr in (64, 128):
+            dv = dk + dr
+        if rng.random() < 0.15:
+            dk, dr, dv = 128, 64, 128
+        rope_dims = dr if rng.random() < 0.7 else int(rng.choice(list(range(2, dr + 1, 2))))
+        sc = None
+        if rng.random() < 0.5:
+            sc = {"factor": float(rng.choice([2.0, 8.0, 40.0])), "original": int(rng.choice([16, 64, 1024])), "fast": float(rng.choice([4.0, 32.0])),
+                  "slow": float(rng.choice([0.5, 1.0]))}
+        kv_from, base = None, float(rng.choice([100.0, 10000.0, 500000.0]))
+        if kind == B and owners and rng.random() < 0.4:
+            kv_from = int(rng.choice(owners))
+            m = layers[kv_from]["mixer"]
+            R, dr, rope_dims, sc, base = m["kv_rank"], m["rot_dim"], m["rot"]["dims"], m["rot"].get("scaling"), m["rot"]["base"]
+        experts, top, ff = None, 1, 8
+        if rng.random() >= 0.2:
+            experts = int(rng.choice([x for x in (1, 2, 3, 4, 8, 16, 33) if x <= E // 2]))
+            top, ff = int(rng.integers(1, min(experts, 4) + 1)), int(rng.choice([8, 24, 64, 128, 192]))
+        layers.append(S.latusun_layer(kind, H, dk, dr, dv, R, experts=experts, top=top, ff=ff, base=base, rope_dims=rope_dims, scaling=sc, kv_from=kv_from,
+                                      scale=float(rng.choice([1.0, 0.5, 0.25])) * (dk + dr) ** -0.5))
+        if kv_from is None and kind == B:
+            owners.append(i)
+    return S.latusun_config(E, V, layers, eps=float(rng.choice([1e-6, 1e-5])), residual_mult=float(rng.choice([0.3, 0.5, 1.0])),
+                            logit_softcap=None if rng.random() < 0.3 else float(rng.choice([5.0, 15.0, 30.0])))

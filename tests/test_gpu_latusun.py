@@ -8,7 +8,7 @@ Where a test plants a key that decides the output, losing that key moves the row
 import numpy as np
 import pytest
 
-from latusun_util import bf16_values, configs, decisive_routing, min_margin, needle_model, oracle, rel_rms, w64
+from latusun_util import bf16_values, configs, decisive_routing, min_margin, needle_model, oracle, random_config, rel_rms, w64
 
 pytestmark = pytest.mark.gpu
 
@@ -179,6 +179,39 @@ def test_tensor_core_shapes(pkg, name, compute):
         assert_rows(np.concatenate(got), ref, TOL[compute], "portions")
     finally:
         plan.free()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_configurations(pkg, seed):
+    """Random layer lists, sizes and constants: the whole prompt, random portions with a decoded tail, and decoding from the first
+    token, in both compute modes."""
+    S, O = pkg.synth, oracle()
+    rng = np.random.default_rng(1000 + seed)
+    cfg = random_config(S, rng)
+    T = int(rng.integers(3, 120))
+    toks = rng.integers(0, cfg["vocab"], T).tolist()
+    for compute in ("float32", "bfloat16"):
+        w = weights(S, cfg, seed, compute)
+        ref = O.forward(cfg, w64(w), toks)
+        if compute == "bfloat16" and min_margin(O, cfg, w, toks) < 0.1:
+            continue
+        batch = int(rng.choice([4, 16, 64, 256]))
+        plan = make_plan(pkg, cfg, w, ctx=T + 3, batch=batch, compute=compute)
+        try:
+            assert_rows(prefill_all(plan, toks, batch), ref, TOL[compute], "whole")
+            got, p = [], 0
+            while p < T - min(T, 5):
+                m = min(int(rng.integers(2, 40)), T - p)
+                got.append(prefill_all(plan, toks[p:p + m], batch, start=p))
+                p += m
+            while p < T:
+                got.append(plan.forward_decode(toks[p], p)[0][None])
+                p += 1
+            assert_rows(np.concatenate(got), ref, TOL[compute], "portions")
+            step = np.stack([plan.forward_decode(t, q)[0] for q, t in enumerate(toks[:40])])
+            assert_rows(step, ref[:40], TOL_DECODE, "decode")
+        finally:
+            plan.free()
 
 
 def test_slots_are_reused_across_requests(pkg):
