@@ -175,8 +175,9 @@ __global__ void __launch_bounds__(256) k_latent_prep(float *__restrict__ P, int 
 // ---------------------------------------------------------------------------------------------------------------------
 // Router: logits z_e = <Wr[e], x> accumulated in FP32 (x FP32 or its BF16 rounding, Wr BF16), scores s_e = sigmoid(z_e), then the
 // `top` largest (the lowest index wins a tie); ids / wts [n][top] in order of falling score.  Four warps per CTA: with
-// rows_per_cta == 4 every warp owns a row (prefill chunks: the router matrix is small and stays in L1 / L2), with
-// rows_per_cta == 1 the four warps share the experts of one row.  Dynamic shared memory: rows_per_cta * (E + experts) floats.
+// rows_per_cta == 4 every warp owns a row, with rows_per_cta == 1 the four warps share the experts of one row (what the plan
+// launches: four times the warps in flight, and the kernel is bound by the latency of its loads; the router matrix is small
+// and stays in L2).  Dynamic shared memory: rows_per_cta * (E + experts) floats.
 template <typename IN_T>
 __global__ void __launch_bounds__(128) k_moe_route(const IN_T *__restrict__ X, const bf16 *__restrict__ Wr, int n, int E, int experts, int top, int rows_per_cta,
                                                    int *__restrict__ ids, float *__restrict__ wts) {
@@ -327,6 +328,20 @@ __global__ void __launch_bounds__(128) k_moe_gather(const bf16 *__restrict__ A, 
     int4 *dst = reinterpret_cast<int4 *>(AS + (size_t)row * E);
     const int4 *src = slot >= 0 ? reinterpret_cast<const int4 *>(A + (size_t)(slot / top) * E) : nullptr;
     for (int i = threadIdx.x; i < E / 8; i += 128) dst[i] = src ? src[i] : make_int4(0, 0, 0, 0);
+}
+
+// The same after the expansions ran on the tcgen05 GEMM (FP32 results KXF [rows][heads * dk], VXF [rows][heads * dv]): BF16 keys
+// [W_uk c_j | rot r_j] per head and BF16 values.  One CTA per cached row.
+__global__ void __launch_bounds__(256) k_latent_pack(const float *__restrict__ KXF, const float *__restrict__ VXF, const bf16 *__restrict__ cache16, int kw, int rank, int dr,
+                                                     int heads, int dk, int dv, bf16 *__restrict__ KX, bf16 *__restrict__ VX) {
+    const int j = blockIdx.x, tid = threadIdx.x, DK = dk + dr;
+    const float *kf = KXF + (size_t)j * heads * dk, *vf = VXF + (size_t)j * heads * dv;
+    bf16 *kx = KX + (size_t)j * heads * DK, *vx = VX + (size_t)j * heads * dv;
+    for (int e = tid; e < heads * DK; e += 256) {
+        const int h = e / DK, d = e % DK;
+        kx[e] = d < dk ? __float2bfloat16_rn(kf[h * dk + d]) : cache16[(size_t)j * kw + rank + d - dk];
+    }
+    for (int e = tid; e < heads * dv; e += 256) vx[e] = __float2bfloat16_rn(vf[e]);
 }
 
 __global__ void __launch_bounds__(256) k_softcap(float *__restrict__ x, long long n, float cap) {

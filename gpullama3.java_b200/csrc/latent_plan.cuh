@@ -223,15 +223,26 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
             // expanded per head (two GEMMs over the BF16 twin of the cache), the rotated shared part is copied behind each head's
             // key, and the tensor-core attention kernel reads [q_u | rot q_r] from the projection rows; gate in its epilogue
             const int DK = s.key_dim + s.rot_dim, M = Y.pf_pos + n;
-            ly::GemmView gv{};
-            gv.lda = L.kw; gv.w_bs = (long long)s.key_dim * s.kv_rank; gv.c_bs = DK;
-            if ((rc = ly_project_view<ly::EPI_STORE>(p, false, M, nullptr, R.kc16, L.w_uk, s.key_dim, s.kv_rank, nullptr, Y.KX16, s.heads * DK, 0, gv, ly::MvView{}, 1, s.heads, 0))) return rc;
-            ly::GemmView gv2{};
-            gv2.lda = L.kw;
-            if ((rc = ly_project_view<ly::EPI_STORE>(p, false, M, nullptr, R.kc16, L.w_uv, L.gd, s.kv_rank, nullptr, Y.VX16, L.gd, 0, gv2, ly::MvView{}, 1, 1, 0))) return rc;
-            const long long cells = (long long)M * s.heads * s.rot_dim;
-            if (cells > 0 && (rc = launch_k(p, false, ly::k_latent_spread, dim3((unsigned)((cells + 255) / 256)), dim3(256), (size_t)0, (const ly::bf16 *)R.kc16, L.kw, s.kv_rank, s.rot_dim,
-                                            s.heads, s.key_dim, Y.KX16, M))) return rc;
+            const LyRun &O = s.kv_from >= 0 ? Y.runs[s.kv_from] : R;
+            if (Y.tc && L.tc_expand && O.tc_lat) {
+                // both expansions on the tcgen05 GEMM (FP32 results), then one pass that rounds them to BF16 and appends the rotated shared part
+                const int mt = (M + 127) / 128;
+                int gr = pg::gemm_launch<pg::GEMM_F32, pg::GEMM_STAGES>(O.m_lat, L.m_xk_b, L.m_xk_b, L.m_xk_c, Y.KXF, s.heads * s.key_dim, M, mt, s.heads * s.key_dim / pg::BN, s.kv_rank, p->stream, pg::FLAVOR_BF16);
+                if (!gr) gr = pg::gemm_launch<pg::GEMM_F32, pg::GEMM_STAGES>(O.m_lat, L.m_xv_b, L.m_xv_b, L.m_xv_c, Y.VXF, L.gd, M, mt, L.gd / pg::BN, s.kv_rank, p->stream, pg::FLAVOR_BF16);
+                if (gr) return fail(p, B200_ERR_CUDA, "tensor-core expansion GEMM launch failed (%d)", gr);
+                if ((rc = launch_k(p, false, ly::k_latent_pack, dim3(M), dim3(256), (size_t)0, (const float *)Y.KXF, (const float *)Y.VXF, (const ly::bf16 *)R.kc16, L.kw, s.kv_rank, s.rot_dim, s.heads,
+                                   s.key_dim, s.value_dim, Y.KX16, Y.VX16))) return rc;
+            } else {
+                ly::GemmView gv{};
+                gv.lda = L.kw; gv.w_bs = (long long)s.key_dim * s.kv_rank; gv.c_bs = DK;
+                if ((rc = ly_project_view<ly::EPI_STORE>(p, false, M, nullptr, R.kc16, L.w_uk, s.key_dim, s.kv_rank, nullptr, Y.KX16, s.heads * DK, 0, gv, ly::MvView{}, 1, s.heads, 0))) return rc;
+                ly::GemmView gv2{};
+                gv2.lda = L.kw;
+                if ((rc = ly_project_view<ly::EPI_STORE>(p, false, M, nullptr, R.kc16, L.w_uv, L.gd, s.kv_rank, nullptr, Y.VX16, L.gd, 0, gv2, ly::MvView{}, 1, 1, 0))) return rc;
+                const long long cells = (long long)M * s.heads * s.rot_dim;
+                if (cells > 0 && (rc = launch_k(p, false, ly::k_latent_spread, dim3((unsigned)((cells + 255) / 256)), dim3(256), (size_t)0, (const ly::bf16 *)R.kc16, L.kw, s.kv_rank, s.rot_dim,
+                                                s.heads, s.key_dim, Y.KX16, M))) return rc;
+            }
             ly::WindowAttn wa{};
             wa.heads = wa.kv_heads = s.heads; wa.dk = DK; wa.dv = s.value_dim; wa.window = s.window; wa.ring = Y.ring; wa.ldk = s.heads * DK; wa.ldv = L.gd;
             wa.scale = s.score_scale; wa.gate = s.gate; wa.gate_off = L.g_off - L.q_off; wa.eps = Y.c.norm_eps;
@@ -284,7 +295,7 @@ static int ly_enqueue_parallel(b200_plan *p, bool decode, int n, const StepState
                 if ((rc = launch_k(p, false, ly::k_moe_topk, dim3(1), dim3(32), (size_t)X * 4, (const float *)Y.ZR, X, top, Y.moe_ids, Y.moe_wts))) return rc;
                 nl += 2;
             } else {
-                const int rpc = n == 1 ? 1 : 4;
+                const int rpc = 1; // a CTA per row: four warps share the row's experts
                 const size_t rsm = (size_t)rpc * (E + X) * 4;
                 if (h16) rc = launch_k(p, false, ly::k_moe_route<ly::bf16>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const ly::bf16 *)Y.A2_16, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts);
                 else rc = launch_k(p, false, ly::k_moe_route<float>, dim3((n + rpc - 1) / rpc), dim3(128), rsm, (const float *)Y.A2_32, (const ly::bf16 *)L.w_router, n, E, X, top, rpc, Y.moe_ids, Y.moe_wts);

@@ -43,6 +43,8 @@ struct LyLayer {
     ly::bf16 *w_router = nullptr;
     // TMA descriptors of the tensor-core prefill (BF16 compute mode, shapes the tcgen05 GEMM tiles cover); *_ok = usable
     CUtensorMap m_proj, m_o, m_gate, m_up, m_down, m_att, m_h;
+    CUtensorMap m_xk_b, m_xv_b, m_xk_c, m_xv_c; // key / value expansion of the BF16 prefill on the tcgen05 GEMM: W_uk, W_uv, FP32 results
+    bool tc_expand = false;
     CUtensorMap m_moe_gate, m_moe_up, m_moe_down, m_moe_h; // mixture of experts on the tcgen05 GEMM: all experts' matrices in one map each
     bool tc_moe = false;
     bool tc_proj = false, tc_o = false, tc_gu = false, tc_down = false;
@@ -52,6 +54,8 @@ struct LyRun {
     bool first = false; // first layer of a loop pass
     float *kc = nullptr, *vc = nullptr;
     ly::bf16 *kc16 = nullptr, *vc16 = nullptr; // BF16 twin rows (BF16 plans whose head sizes the tensor-core attention takes)
+    CUtensorMap m_lat;                         // latent attention: the latent columns of the BF16 twin rows as a GEMM operand
+    bool tc_lat = false;
     int kw = 0, vw = 0;                        // floats per cache row (latent attention: one cache, kw = kv_rank + rot_dim, vc == nullptr)
     bool own = true;                           // false: kc is the cache of the run this layer reads (kv_from)
 };
@@ -80,6 +84,7 @@ struct Layered {
     float *final_norm_b = nullptr;
     float *A2_32 = nullptr, *Q = nullptr, *LAT32 = nullptr, *YS = nullptr, *moe_wts = nullptr, *ZR = nullptr;
     ly::bf16 *A2_16 = nullptr, *QU16 = nullptr, *LAT16 = nullptr;
+    float *KXF = nullptr, *VXF = nullptr;      // FP32 results of the tcgen05 expansions, rows padded to whole 128-row tiles
     ly::bf16 *KX16 = nullptr, *VX16 = nullptr; // keys / values of one layer expanded per head for a prefill chunk: [context][heads * size]
     int maxKX = 0, maxVX = 0, pf_pos = 0;      // pf_pos: first position of the chunk being enqueued
     // expert-sorted, tile-padded operands of the tcgen05 expert projections (BF16 prefill)
@@ -336,6 +341,20 @@ static int ly_tc_init(b200_plan *p) {
             L.tc_gu = fits(F, E) && L.s.ff_act == B200_ACT_GELU_TANH && pg::make_map(&L.m_gate, L.w_gu, F, E, 128) == 0 &&
                       pg::make_map(&L.m_up, L.w_gu + (size_t)F * E, F, E, 128) == 0;
             L.tc_down = fits(E, F) && pg::make_map(&L.m_down, L.w_down, E, F, 128) == 0 && pg::make_map(&L.m_h, Y.H16, rows, F, pg::BM) == 0;
+        }
+    }
+    if (Y.KXF) { // key / value expansions: A = latent columns of a cache's BF16 twin rows, B = W_uk / W_uv as stored, C = FP32 scratch
+        const uint64_t rowsX = ((uint64_t)Y.ring + 127) / 128 * 128;
+        for (LyRun &R : Y.runs) {
+            const LyLayer &L = Y.layers[R.layer];
+            R.tc_lat = R.own && R.kc16 && L.kw % 8 == 0 && L.s.kv_rank % 64 == 0 && pg::make_map_ld(&R.m_lat, R.kc16, (uint64_t)Y.ring, L.s.kv_rank, L.kw, pg::BM) == 0;
+        }
+        for (size_t r = 0; r < Y.runs.size(); r++) {
+            LyLayer &L = Y.layers[Y.runs[r].layer];
+            const LyRun &O = L.s.kv_from >= 0 ? Y.runs[L.s.kv_from] : Y.runs[r];
+            const uint64_t nk = (uint64_t)L.s.heads * L.s.key_dim, nv = (uint64_t)L.gd, K = L.s.kv_rank;
+            L.tc_expand = L.expand && O.tc_lat && nk % 128 == 0 && nv % 128 == 0 && pg::make_map(&L.m_xk_b, L.w_uk, nk, K, pg::BN) == 0 &&
+                          pg::make_map(&L.m_xv_b, L.w_uv, nv, K, pg::BN) == 0 && pg::make_map_c(&L.m_xk_c, Y.KXF, rowsX, nk) == 0 && pg::make_map_c(&L.m_xv_c, Y.VXF, rowsX, nv) == 0;
         }
     }
     if (Y.AS16 && pg::make_map(&Y.m_as, Y.AS16, (uint64_t)Y.max_tiles128 * 128, E, pg::BM) == 0 && pg::make_map_c(&Y.m_ysp, Y.YSP, (uint64_t)Y.max_tiles128 * 128, E) == 0)
@@ -603,6 +622,9 @@ static int ly_build(b200_plan *p, const b200_layered_config *cfg, const b200_lay
         if (Y.maxKX > 0) {
             if ((rc = dalloc(p, &Y.KX16, (size_t)Y.ring * Y.maxKX * 2))) return rc;
             if ((rc = dalloc(p, &Y.VX16, (size_t)Y.ring * Y.maxVX * 2))) return rc;
+            const size_t rowsX = ((size_t)Y.ring + 127) / 128 * 128;
+            if ((rc = dalloc(p, &Y.KXF, rowsX * Y.maxKX * 4))) return rc;
+            if ((rc = dalloc(p, &Y.VXF, rowsX * Y.maxVX * 4))) return rc;
         }
         if ((rc = dalloc(p, &Y.A2_32, rows32 * E * 4))) return rc;
         if ((rc = dalloc(p, &Y.Q, cap * Y.maxQ * 4))) return rc;

@@ -644,6 +644,19 @@ inline int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t 
     return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// A column block of a wider row-major matrix: K columns of rows that are ld elements apart (ld * 2 bytes a multiple of 16).
+inline int make_map_ld(CUtensorMap *map, const void *base, uint64_t rows, uint64_t K, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 // C / x as [rows][cols] fp32 row-major, box = 32 columns (128 bytes) x 128 rows, 128-byte swizzle (matches the epilogue's staging)
 inline int make_map_c(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols) {
     EncodeTiledFn fn = encode_fn();

@@ -53,10 +53,11 @@ def configs(S):
         "tiles128": S.latusun_config(128, 200, [
             L(B, 2, 96, 32, 128, 64, experts=3, top=2, ff=64), L(A, 3, 96, 32, 128, 40, experts=None, scaling=BLEND),
             L(B, 1, 96, 32, 128, 64, experts=2, top=1, ff=32, kv_from=0)], residual_mult=0.6, logit_softcap=12.0),
-        # key size 192, value size 128: the third instance
+        # key size 192, value size 128: the third instance; layers 0 and 2 (latent of 64, 256 key and value columns) expand keys and
+        # values on the tcgen05 GEMM, layer 1 on the any-shape kernel
         "tiles192": S.latusun_config(128, 160, [
-            L(B, 2, 128, 64, 128, 48, experts=2, top=1, ff=64), L(A, 1, 128, 64, 128, 40, experts=None, scaling=BLEND),
-            L(B, 2, 128, 64, 128, 48, experts=None, kv_from=0)], residual_mult=0.6, logit_softcap=None),
+            L(B, 2, 128, 64, 128, 64, experts=2, top=1, ff=64), L(A, 1, 128, 64, 128, 40, experts=None, scaling=BLEND),
+            L(B, 2, 128, 64, 128, 64, experts=None, kv_from=0)], residual_mult=0.6, logit_softcap=None),
     }
 
 
