@@ -271,7 +271,8 @@ int b200_kv_reset(b200_plan *plan);
 
 /* Test/diagnostic read-back of a named device buffer into host memory.  Names:
  * "x","xb","q","k","v","hb","logits","key_cache","value_cache","xq","xs".  `layer` selects the
- * layer for the KV caches (ignored otherwise).  Copies min(bytes, buffer size). */
+ * layer for the KV caches (ignored otherwise).  Copies min(bytes, buffer size).  Layered plans: `layer` is the layer RUN;
+ * a latent-attention run has ONE cache, "key_cache" = rows [latent | rotated shared key part], and no "value_cache". */
 int b200_read_buffer(b200_plan *plan, const char *name, int32_t layer, void *dst, size_t bytes);
 
 /* Measurement hook for bench.py's roofline line: launches ONE kernel family of the decode step
